@@ -1,0 +1,388 @@
+"""CPU oracle for the Quartet MXFP4 QuantizedLinear path.
+
+TEST INFRASTRUCTURE ONLY.  Nothing in the shipped package imports this file;
+only the tests, the smoke check and the benchmark's CPU-baseline leg do.
+
+This is a from-scratch restatement, in fp32 torch ops on CPU tensors, of the
+arithmetic the reference performs:
+
+* quantizer math            src/models/quantization/quantizers/mxfp4_triton.py:33-174
+* which tensor is quantized src/models/quantization/backward.py:57-85
+  along which axis
+* quantizer STE backward    src/models/quantization/quantizers/mxfp4.py:142-146
+* packed formats            notebooks/benchmark_mxfp4.ipynb:881-979 (register_fake
+  (e2m1 nibbles, E8M0,        shape contracts) -- the reference itself never
+  blocked scale layout,       materialises codes or scale bytes, so this file
+  bit-packed clip mask)       derives them from the same intermediate values.
+* `tl.rand`                 third-party: triton 3.6.0, triton/language/random.py
+                            (Philox4x32-10, key = 64-bit seed, counter =
+                            (offset, 0, 0, 0), first output word -> [0, 1)).
+
+Parity pin: `tests/golden/*.npz` hold outputs of the reference's own kernel run
+under the Triton interpreter (generator: tests/golden/make_golden.py); the
+CPU test-suite checks every function here against them bit for bit.
+"""
+from __future__ import annotations
+
+import math
+
+import numpy as np
+import torch
+
+GROUP = 32
+# e2m1 magnitudes by 3-bit index (code bit 3 is the sign).
+E2M1_GRID = (0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0)
+QUEST_GAUSSIAN_SCALE = 2.92247856 / 6.0  # mxfp4.py:136
+SR_ALPHA = 4.0 / 3.0  # each absmax-scaled operand carries 1/(3/4), mxfp4_triton.py:60
+
+PHILOX_KEY_A = 0x9E3779B9
+PHILOX_KEY_B = 0xBB67AE85
+PHILOX_ROUND_A = 0xD2511F53
+PHILOX_ROUND_B = 0xCD9E8D57
+
+
+# ----------------------------------------------------------------------------
+# rotation matrix
+# ----------------------------------------------------------------------------
+def hadamard32(dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
+    """Normalised 32x32 Sylvester Hadamard matrix, rounded to `dtype`, as fp32.
+
+    The reference builds it with fast_hadamard_transform on an identity
+    (mxfp4.py:42-44, 154-156) and then casts it to the activation dtype
+    (mxfp4.py:49, 160); the notebook equates it with scipy.linalg.hadamard
+    (benchmark_mxfp4.ipynb:36-39).
+    """
+    h = torch.ones(1, 1, dtype=torch.float64)
+    while h.shape[0] < GROUP:
+        h = torch.cat([torch.cat([h, h], 1), torch.cat([h, -h], 1)], 0)
+    h = (h * GROUP ** -0.5).to(torch.float32)
+    return h.to(dtype).to(torch.float32)
+
+
+def signs_to_diag(signs: int) -> torch.Tensor:
+    """bit j of `signs` set -> column j of the rotation is negated (H @ diag(s))."""
+    return torch.tensor([-1.0 if (signs >> j) & 1 else 1.0 for j in range(GROUP)], dtype=torch.float32)
+
+
+def rotate(x: torch.Tensor, h: torch.Tensor) -> torch.Tensor:
+    """`x.view(-1, 32) @ H` with fp32 accumulation (mxfp4_triton.py:46-47)."""
+    return (x.to(torch.float32).reshape(-1, GROUP) @ h.to(torch.float32)).contiguous()
+
+
+# ----------------------------------------------------------------------------
+# Philox (triton-compatible) and the library's own dither stream
+# ----------------------------------------------------------------------------
+def _mulhilo(a: int, b: np.ndarray):
+    p = np.uint64(a) * b.astype(np.uint64)
+    return (p >> np.uint64(32)).astype(np.uint32), (p & np.uint64(0xFFFFFFFF)).astype(np.uint32)
+
+
+def philox4x32(c0, c1, c2, c3, k0: int, k1: int, rounds: int = 10):
+    """Philox4x32 with Triton's word order (triton/language/random.py:13-41)."""
+    c0 = np.asarray(c0, dtype=np.uint32)
+    c1 = np.broadcast_to(np.asarray(c1, dtype=np.uint32), c0.shape)
+    c2 = np.broadcast_to(np.asarray(c2, dtype=np.uint32), c0.shape)
+    c3 = np.broadcast_to(np.asarray(c3, dtype=np.uint32), c0.shape)
+    k0 = np.uint32(k0 & 0xFFFFFFFF)
+    k1 = np.uint32(k1 & 0xFFFFFFFF)
+    with np.errstate(over="ignore"):
+        for _ in range(rounds):
+            hi_b, lo_b = _mulhilo(PHILOX_ROUND_B, c2)
+            hi_a, lo_a = _mulhilo(PHILOX_ROUND_A, c0)
+            c0, c2 = hi_b ^ c1 ^ k0, hi_a ^ c3 ^ k1
+            c1, c3 = lo_b, lo_a
+            k0 = np.uint32((int(k0) + PHILOX_KEY_A) & 0xFFFFFFFF)
+            k1 = np.uint32((int(k1) + PHILOX_KEY_B) & 0xFFFFFFFF)
+    return c0, c1, c2, c3
+
+
+def triton_rand(seed: int, offsets: np.ndarray) -> torch.Tensor:
+    """`tl.rand(seed, offsets)` (triton/language/random.py:113-157), fp32 in [0, 1)."""
+    offs = np.asarray(offsets).astype(np.int64)
+    lo = (offs & 0xFFFFFFFF).astype(np.uint32)
+    w0, _, _, _ = philox4x32(lo, 0, 0, 0, seed & 0xFFFFFFFF, (seed >> 32) & 0xFFFFFFFF)
+    x = w0.view(np.int32).astype(np.int64)
+    x = np.where(x < 0, -x - 1, x)
+    u = x.astype(np.float32) * np.float32(4.6566127342e-10)
+    return torch.from_numpy(u.astype(np.float32))
+
+
+def own_dither_bytes(seed: int, offset: int, n_groups: int) -> np.ndarray:
+    """The library's own stochastic-rounding stream: 8 dither bits per element.
+
+    Group g (32 elements, numbered in the OUTPUT tensor's row-major order) uses
+    two Philox4x32-10 calls with key = seed, counter = (2g + j, g_hi, offset_lo,
+    offset_hi), j = 0, 1.  Call j covers elements 16j .. 16j+15 of the group;
+    element 16j + 4w + b takes byte b (little end first) of output word w.
+    Returns uint8 [n_groups, 32].
+    """
+    g = np.arange(n_groups, dtype=np.uint64)
+    out = np.empty((n_groups, 32), dtype=np.uint8)
+    for j in range(2):
+        ctr = g * np.uint64(2) + np.uint64(j)
+        words = philox4x32(
+            (ctr & np.uint64(0xFFFFFFFF)).astype(np.uint32),
+            (ctr >> np.uint64(32)).astype(np.uint32),
+            np.uint32(offset & 0xFFFFFFFF),
+            np.uint32((offset >> 32) & 0xFFFFFFFF),
+            seed & 0xFFFFFFFF,
+            (seed >> 32) & 0xFFFFFFFF,
+        )
+        for w in range(4):
+            for b in range(4):
+                out[:, 16 * j + 4 * w + b] = ((words[w] >> np.uint32(8 * b)) & np.uint32(0xFF)).astype(np.uint8)
+    return out
+
+
+# ----------------------------------------------------------------------------
+# rounding onto the e2m1 grid
+# ----------------------------------------------------------------------------
+def _ladder(a: torch.Tensor, thresholds) -> torch.Tensor:
+    """index = number of thresholds strictly below `a` (NaN -> 0)."""
+    idx = torch.zeros_like(a, dtype=torch.int32)
+    for t in thresholds:
+        idx += (a > t).to(torch.int32)
+    return idx
+
+
+_RTN_THRESHOLDS = (0.25, 0.75, 1.25, 1.75, 2.5, 3.5, 5.0)  # mxfp4_triton.py:131-159
+_SR_THRESHOLDS = (0.5, 1.0, 1.5, 2.0, 3.0, 4.0)  # mxfp4_triton.py:71-121
+_GRID_T = torch.tensor(E2M1_GRID, dtype=torch.float32)
+
+
+def rtn_index(a: torch.Tensor) -> torch.Tensor:
+    """Round-to-nearest with ties toward the smaller magnitude (strict `>`)."""
+    return _ladder(a, _RTN_THRESHOLDS)
+
+
+def sr_index(a: torch.Tensor, u: torch.Tensor) -> torch.Tensor:
+    """Stochastic rounding with the reference's `u < p` rule (mxfp4_triton.py:123-129)."""
+    lo_idx = _ladder(a, _SR_THRESHOLDS)  # 0..6
+    lo = _GRID_T[lo_idx.long()]
+    hi = _GRID_T[(lo_idx + 1).long()]
+    p = (a - lo) / (hi - lo)
+    return lo_idx + (u < p).to(torch.int32)
+
+
+def sr_index_own(a: torch.Tensor, dither: torch.Tensor) -> torch.Tensor:
+    """Stochastic rounding as the library's own stream does it.
+
+    `a` = |v| with v = xh * (0.75 * 2^-e) (a multiply, not the reference's
+    division).  Values below 1 are shifted by +1 so that the grid step is
+    bit 22 of the fp32 pattern everywhere, then `(dither << 14) + (1 << 13)`
+    is added to the bit pattern and the low 22 bits are dropped.
+    """
+    small = a < 1.0
+    t = torch.where(small, a + 1.0, a)
+    bits = t.contiguous().view(torch.int32).to(torch.int64)
+    bits = bits + (dither.to(torch.int64) << 14) + (1 << 13)
+    top = bits >> 22
+    idx = top - 252 - torch.where(small, 2, 0)
+    return idx.to(torch.int32)
+
+
+# ----------------------------------------------------------------------------
+# the two quantizers
+# ----------------------------------------------------------------------------
+class Quantized:
+    """Result of one quantizer call on a [rows, cols] tensor (groups along cols)."""
+
+    def __init__(self, rows, cols, idx, neg, e8m0, shared, mask=None, scale=1.0):
+        self.rows, self.cols = rows, cols
+        self.idx = idx  # int32 [rows, cols]   magnitude index 0..7
+        self.neg = neg  # bool  [rows, cols]   sign bit (reference: not (v > 0))
+        self.e8m0 = e8m0  # uint8 [rows, cols/32]
+        self.shared = shared  # fp32 [rows, cols/32]  the reference's `shared_exps`
+        self.mask = mask  # bool [rows, cols] or None
+        self.scale = scale  # value = grid[idx] * 2^(e8m0-127) * scale
+
+    @property
+    def codes(self) -> torch.Tensor:
+        """uint8 [rows, cols] nibble values: sign << 3 | idx."""
+        return (self.idx + 8 * self.neg.to(torch.int32)).to(torch.uint8)
+
+    def packed(self) -> torch.Tensor:
+        """uint8 [rows, cols/2]; even element in the low nibble (benchmark_mxfp4.ipynb:912-914)."""
+        c = self.codes
+        return (c[:, 0::2] | (c[:, 1::2] << 4)).contiguous()
+
+    def packed_mask(self) -> torch.Tensor:
+        """uint8 [rows, cols/8], LSB first (benchmark_mxfp4.ipynb:918, 975-979)."""
+        m = self.mask.to(torch.uint8).reshape(self.rows, self.cols // 8, 8)
+        w = torch.tensor([1, 2, 4, 8, 16, 32, 64, 128], dtype=torch.uint8)
+        return (m * w).sum(-1).to(torch.uint8)
+
+    def dequant(self) -> torch.Tensor:
+        """What the reference kernel stores: q * sign * shared_exps (mxfp4_triton.py:168-174)."""
+        q = _GRID_T[self.idx.long()] * torch.where(self.neg, -1.0, 1.0)
+        return (q.reshape(self.rows, -1, GROUP) * self.shared.unsqueeze(-1)).reshape(self.rows, self.cols)
+
+    def dequant_from_bytes(self) -> torch.Tensor:
+        """grid[idx] * 2^(e8m0-127) * scale -- what the packed format means."""
+        q = _GRID_T[self.idx.long()] * torch.where(self.neg, -1.0, 1.0)
+        s = torch.exp2(self.e8m0.to(torch.float32) - 127.0) * self.scale
+        return (q.reshape(self.rows, -1, GROUP) * s.unsqueeze(-1)).reshape(self.rows, self.cols)
+
+
+def _exp_byte(e: torch.Tensor) -> torch.Tensor:
+    return torch.clamp(e + 127.0, 0, 254).nan_to_num(0.0).to(torch.uint8)
+
+
+def quant_fwd(x: torch.Tensor, h: torch.Tensor, gaussian_scale: float = QUEST_GAUSSIAN_SCALE) -> Quantized:
+    """Forward quantizer: branch quest=True, stochastic_round=False (mxfp4_triton.py:33-57, 130-174)."""
+    rows, cols = x.shape
+    xh = rotate(x, h)  # [groups, 32]
+    mean_sq = (xh * xh).sum(-1, keepdim=True) / GROUP
+    mean = xh.sum(-1, keepdim=True) / GROUP
+    std = torch.sqrt(mean_sq - mean * mean)
+    scales = gaussian_scale * std + 1e-8
+    e = torch.floor(torch.log2(scales))
+    shared = torch.exp2(e)
+    v = xh / shared
+    a = v.abs()
+    idx = rtn_index(a)
+    neg = ~(v > 0)
+    mask = a < 6
+    g = cols // GROUP
+    return Quantized(rows, cols, idx.reshape(rows, cols), neg.reshape(rows, cols), _exp_byte(e).reshape(rows, g),
+                     shared.reshape(rows, g), mask.reshape(rows, cols), 1.0)
+
+
+def quant_bwd(x: torch.Tensor, h: torch.Tensor, noise: torch.Tensor | None, stochastic: bool = True) -> Quantized:
+    """Backward quantizer: branch quest=False (mxfp4_triton.py:58-61, 70-129).
+
+    `noise` is indexed like `x` (row-major over the tensor the kernel sees);
+    `stochastic=False` gives the round-to-nearest variant used by
+    AlbertTsengQuantizer(stochastic=False) / AlignedAlbertTsengQuantizer.
+    """
+    rows, cols = x.shape
+    xh = rotate(x, h)
+    amax = xh.abs().amax(-1, keepdim=True)
+    e = torch.floor(torch.log2(amax)) - 2
+    shared = torch.exp2(e) / 0.75
+    v = xh / shared
+    a = v.abs()
+    if stochastic:
+        idx = sr_index(a, noise.reshape(-1, GROUP).to(torch.float32))
+    else:
+        idx = rtn_index(a)
+    neg = ~(v > 0)
+    g = cols // GROUP
+    return Quantized(rows, cols, idx.reshape(rows, cols), neg.reshape(rows, cols), _exp_byte(e).reshape(rows, g),
+                     shared.reshape(rows, g), None, SR_ALPHA)
+
+
+def quant_bwd_own(x: torch.Tensor, h_base: torch.Tensor, signs: int, seed: int, offset: int) -> Quantized:
+    """Backward quantizer with the library's own Philox dither stream.
+
+    Same scale rule as `quant_bwd`; differs in (i) v = xh * (0.75 * 2^-e)
+    instead of a division by fl(2^e / 0.75), (ii) the dither-and-truncate
+    rounding of `sr_index_own`, (iii) the sign vector applied as a sign-bit flip
+    (exactly equivalent to rotating with H @ diag(s)).
+    """
+    rows, cols = x.shape
+    xh = rotate(x, h_base)
+    amax = xh.abs().amax(-1, keepdim=True)
+    e = torch.floor(torch.log2(amax)) - 2
+    inv = torch.exp2(-e) * 0.75
+    v = xh * inv
+    a = v.abs()
+    n_groups = xh.shape[0]
+    dither = torch.from_numpy(own_dither_bytes(seed, offset, n_groups).astype(np.int64))
+    idx = sr_index_own(a, dither)
+    zero_group = (amax == 0).expand_as(a)
+    idx = torch.where(zero_group, torch.zeros_like(idx), idx)
+    flip = torch.tensor([bool((signs >> j) & 1) for j in range(GROUP)])
+    neg = (~(v > 0)) ^ flip
+    g = cols // GROUP
+    shared = torch.exp2(e) / 0.75
+    return Quantized(rows, cols, idx.reshape(rows, cols), neg.reshape(rows, cols), _exp_byte(e).reshape(rows, g),
+                     shared.reshape(rows, g), None, SR_ALPHA)
+
+
+# ----------------------------------------------------------------------------
+# blocked scale layout (128 x 4 tiles of 512 bytes)
+# ----------------------------------------------------------------------------
+def pad_up(v: int, m: int) -> int:
+    return (v + m - 1) // m * m
+
+
+def sf_offset(row: int, kblock: int, padded_kblocks: int) -> int:
+    """Byte offset of scale (row, kblock) in the blocked layout the block-scaled
+    MMA consumes (`to_blocked` call sites benchmark_mxfp4.ipynb:1015-1016; shape
+    contract :909-917)."""
+    block = (row // 128) * (padded_kblocks // 4) + kblock // 4
+    r = row % 128
+    return block * 512 + (r % 32) * 16 + (r // 32) * 4 + kblock % 4
+
+
+def to_blocked(e8m0: torch.Tensor) -> torch.Tensor:
+    """[rows, kblocks] uint8 -> flat blocked buffer of pad128(rows) * pad4(kblocks) bytes."""
+    rows, kb = e8m0.shape
+    pr, pk = pad_up(rows, 128), pad_up(kb, 4)
+    t = torch.zeros(pr, pk, dtype=torch.uint8)
+    t[:rows, :kb] = e8m0
+    t = t.reshape(pr // 128, 4, 32, pk // 4, 4).permute(0, 3, 2, 1, 4)
+    return t.contiguous().reshape(-1)
+
+
+def from_blocked(buf: torch.Tensor, rows: int, kb: int) -> torch.Tensor:
+    pr, pk = pad_up(rows, 128), pad_up(kb, 4)
+    t = buf.reshape(pr // 128, pk // 4, 32, 4, 4).permute(0, 3, 2, 1, 4).reshape(pr, pk)
+    return t[:rows, :kb].contiguous()
+
+
+# ----------------------------------------------------------------------------
+# the layer: forward, backward (QEQWtt_QEtQXttFn + quantizer STE backward)
+# ----------------------------------------------------------------------------
+def unrotate_mask(g: torch.Tensor, mask: torch.Tensor, h: torch.Tensor) -> torch.Tensor:
+    """`((g * mask).view(-1, 32) @ H.T).view(shape)` (mxfp4.py:142-146)."""
+    shape = g.shape
+    return ((g.to(torch.float32) * mask.to(torch.float32)).reshape(-1, GROUP) @ h.T).reshape(shape)
+
+
+def linear_forward(x, w, h_f):
+    """QuantizedLinear.forward (quantization/__init__.py:36-42) with the Quest quantizer on both operands."""
+    xq = quant_fwd(x, h_f)
+    wq = quant_fwd(w, h_f)
+    y = xq.dequant() @ wq.dequant().T
+    return y, xq, wq
+
+
+def linear_backward(e, xq: Quantized, wq: Quantized, h_f, h_b, noises=None, seeds=None):
+    """QEQWtt_QEtQXttFn.backward (backward.py:64-85) followed by the two
+    QuestMXFP4QuantizerFn.backward calls (mxfp4.py:142-146).
+
+    `noises` = 4 tensors (for E, Wq^T, E^T, Xq^T, in the reference's call
+    order) or `seeds` = 4 ints for `triton_rand`.
+    """
+    xd, wd = xq.dequant(), wq.dequant()
+    ops = [e, wd.T.contiguous(), e.T.contiguous(), xd.T.contiguous()]
+    qs = []
+    for i, t in enumerate(ops):
+        if noises is not None:
+            u = noises[i]
+        else:
+            u = triton_rand(seeds[i], np.arange(t.numel())).reshape(t.shape)
+        qs.append(quant_bwd(t, h_b, u))
+    eq, wtq, etq, xtq = qs
+    grad_xq = eq.dequant() @ wtq.dequant().T
+    grad_wq = etq.dequant() @ xtq.dequant().T
+    dx = unrotate_mask(grad_xq, xq.mask, h_f)
+    dw = unrotate_mask(grad_wq, wq.mask, h_f)
+    return dx, dw, (eq, wtq, etq, xtq), (grad_xq, grad_wq)
+
+
+def layer_flops(m: int, n: int, k: int) -> float:
+    return 6.0 * m * n * k
+
+
+def cpu_layer_fwd_bwd(x, w, e, seed: int = 0):
+    """One pseudo-quantized QuantizedLinear forward + backward with torch.rand
+    noise; used as the timed CPU baseline."""
+    h_f = hadamard32(torch.bfloat16)
+    gen = torch.Generator().manual_seed(seed)
+    y, xq, wq = linear_forward(x, w, h_f)
+    noises = [torch.rand(s, generator=gen) for s in (e.shape, (w.shape[1], w.shape[0]), (e.shape[1], e.shape[0]), (x.shape[1], x.shape[0]))]
+    dx, dw, _, _ = linear_backward(e, xq, wq, h_f, h_f, noises=noises)
+    return y, dx, dw
