@@ -1,0 +1,150 @@
+/*
+ * quartet_b200 -- C ABI of the B200 (sm_100a) MXFP4 quantized-linear path.
+ *
+ * Every entry point takes raw DEVICE pointers, extents and a CUDA stream
+ * (a cudaStream_t passed as void*; NULL = the legacy default stream).  The
+ * caller owns every buffer; no call allocates device memory.  Calls return 0
+ * on success and a negative QUARTET_E_* code on rejection (nothing was
+ * launched); quartet_last_error_string() describes the last rejection on the
+ * calling thread.  Nothing throws, aborts or traps.
+ *
+ * Data formats (pinned by the reference's real-quantized op contracts,
+ * notebooks/benchmark_mxfp4.ipynb:881-979):
+ *   codes  uint8 [rows, cols/2]   two e2m1 codes per byte, even element in the
+ *                                 low nibble; code = sign<<3 | index into
+ *                                 {0, .5, 1, 1.5, 2, 3, 4, 6}
+ *   sf     uint8, E8M0 (value 2^(b-127)), one per 32 elements of a row, stored
+ *          in 512-byte blocks of 128 rows x 4 scales; logical shape
+ *          [pad128(rows), pad4(cols/32)]; byte offset = quartet_sf_offset()
+ *   mask   uint8 [rows, cols/8]   1 bit per element, LSB first; 1 = |v| < 6
+ *
+ * Reference paths are given relative to the reference project root.
+ */
+#ifndef QUARTET_B200_H
+#define QUARTET_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef void* quartet_stream_t;
+
+enum {
+    QUARTET_OK = 0,
+    QUARTET_E_NULL = -1,      /* a required pointer is NULL */
+    QUARTET_E_SHAPE = -2,     /* extent not supported (see each call) */
+    QUARTET_E_ALIGN = -3,     /* pointer not 16-byte aligned */
+    QUARTET_E_ARG = -4,       /* bad enum / flag value */
+    QUARTET_E_CUDA = -5,      /* a CUDA runtime/driver call failed */
+    QUARTET_E_DEVICE = -6     /* not an sm_100 device */
+};
+
+enum { QUARTET_BF16 = 0, QUARTET_F32 = 1 };
+
+/* rounding modes of the backward (absmax-scaled) quantizers */
+enum {
+    QUARTET_ROUND_NEAREST = 0,    /* AlbertTsengQuantizer(stochastic=False) */
+    QUARTET_ROUND_SR_PHILOX = 1,  /* stochastic, library's own Philox4x32-10 dither stream (seed, offset) */
+    QUARTET_ROUND_SR_NOISE = 2,   /* stochastic, caller-supplied fp32 uniform noise tensor, reference `u < p` rule */
+    QUARTET_ROUND_SR_TLRAND = 3   /* stochastic, reference-compatible stream: tl.rand(seed, flat_offset) */
+};
+
+/*
+ * Forward quantizer: 32-point Hadamard rotation along `cols`, std-based scale,
+ * round to nearest, clip mask.
+ * Replaces mxfp4_forward_kernel with quest=True, stochastic_round=False
+ * (src/models/quantization/quantizers/mxfp4_triton.py:33-57,130-174) as called by
+ * QuestMXFP4QuantizerFn.forward (src/models/quantization/quantizers/mxfp4.py:129-140);
+ * output contract = fusedQuantizeMx (notebooks/benchmark_mxfp4.ipynb:897-921).
+ * x: [rows, cols] row-major, dtype QUARTET_BF16 / QUARTET_F32; cols % 128 == 0, rows >= 1.
+ * had_scale: magnitude of the rotation matrix entries (bf16(32^-1/2) = 0.1767578125 when the
+ * reference has cast H to bf16, 32^-1/2 in fp32 otherwise).  mask may be NULL.
+ */
+int quartet_quant_fwd(const void* x, int x_dtype, int64_t rows, int64_t cols, float had_scale, float gaussian_scale,
+                      uint8_t* codes, uint8_t* sf, uint8_t* mask, quartet_stream_t stream);
+
+/*
+ * Backward quantizer, row-wise: rotation (H @ diag(signs)), absmax scale
+ * E8M0 = floor(log2 amax) - 2, rounding per `rounding`.  The 4/3 of the reference's
+ * shared exponent (2^e / 0.75) is NOT in the scale bytes; fold it into the GEMM alpha.
+ * Replaces mxfp4_forward_kernel with quest=False (mxfp4_triton.py:58-61,70-129) as called by
+ * AlbertTsengQuantizerFn.forward (mxfp4.py:17-28) on `e` (src/models/quantization/backward.py:72).
+ * signs: bit j set = coefficient j of every group negated; if signs_dev != NULL the kernel
+ * reads the word from device memory instead (no host sync after re_randomize, mxfp4.py:52-60).
+ * noise: fp32 [rows, cols], only for QUARTET_ROUND_SR_NOISE.
+ */
+int quartet_quant_bwd(const void* x, int x_dtype, int64_t rows, int64_t cols, float had_scale, uint32_t signs,
+                      const uint32_t* signs_dev, int rounding, uint64_t seed, uint64_t offset, const float* noise,
+                      uint8_t* codes, uint8_t* sf, quartet_stream_t stream);
+
+/*
+ * Backward quantizer of the TRANSPOSE: groups of 32 run along `rows` of x; writes
+ * codes_t [cols, rows/2] and sf_t (logical [cols, rows/32]).
+ * Replaces `g_quantizer(e.reshape(M,-1).T.contiguous())` (backward.py:81); contract =
+ * backward_t_bf16 (benchmark_mxfp4.ipynb:924-937).  rows % 128 == 0, cols % 128 == 0.
+ * noise (QUARTET_ROUND_SR_NOISE) and the QUARTET_ROUND_SR_TLRAND offsets index the
+ * transposed tensor [cols, rows] row-major, as the reference kernel would see it.
+ */
+int quartet_quant_bwd_t(const void* x, int x_dtype, int64_t rows, int64_t cols, float had_scale, uint32_t signs,
+                        const uint32_t* signs_dev, int rounding, uint64_t seed, uint64_t offset, const float* noise,
+                        uint8_t* codes_t, uint8_t* sf_t, quartet_stream_t stream);
+
+/*
+ * De-quantize + transpose + backward-quantize of an MXFP4 tensor.
+ * Replaces `g_quantizer(w.T.contiguous())` / `g_quantizer(x.reshape(M,-1).T.contiguous())`
+ * (backward.py:73,82) on the saved forward-quantized operands; contract = backward_qt_bf16
+ * (benchmark_mxfp4.ipynb:940-957).  Input value = grid[code] * 2^(sf-127) * in_scale.
+ * rows % 128 == 0, cols % 128 == 0.
+ */
+int quartet_requant_t(const uint8_t* codes, const uint8_t* sf, int64_t rows, int64_t cols, float in_scale,
+                      float had_scale, uint32_t signs, const uint32_t* signs_dev, int rounding, uint64_t seed,
+                      uint64_t offset, const float* noise, uint8_t* codes_t, uint8_t* sf_t, quartet_stream_t stream);
+
+/*
+ * Block-scaled MXFP4 GEMM, D[M,N] = alpha * A[M,K] . B[N,K]^T, both operands K-major.
+ * Replaces F.linear(xq, wq) (backward.py:62), F.linear(Q(e), Q(w^T)) (backward.py:71-75) and
+ * einsum("ib,jb->ij", Q(e^T), Q(x^T)) (backward.py:79-83); contract = matmul_mxf4_bf16_tn
+ * (benchmark_mxfp4.ipynb:882-895).  M, N, K % 128 == 0.
+ * If mask != NULL ([M, N/8] bits), the epilogue also applies the forward quantizer's
+ * straight-through backward, ((alpha*acc) * mask).view(-1,32) @ H^T (mxfp4.py:142-146),
+ * with H = had_scale * Sylvester-32.  d_dtype: QUARTET_BF16 or QUARTET_F32.
+ */
+int quartet_gemm_mxfp4_tn(const uint8_t* a, const uint8_t* a_sf, const uint8_t* b, const uint8_t* b_sf, int64_t M,
+                          int64_t N, int64_t K, float alpha, const uint8_t* mask, float had_scale, void* d,
+                          int d_dtype, quartet_stream_t stream);
+
+/*
+ * Stand-alone straight-through backward of the forward quantizer:
+ * out = ((g * mask).view(-1,32) @ H^T).view(rows, cols)  (mxfp4.py:142-146); mask NULL = all ones
+ * (AlbertTsengQuantizerFn.backward, mxfp4.py:30-34).  cols % 32 == 0.
+ */
+int quartet_unrotate_mask(const void* g, int g_dtype, const uint8_t* mask, int64_t rows, int64_t cols, float had_scale,
+                          void* out, int out_dtype, quartet_stream_t stream);
+
+/*
+ * codes + scales -> values (still in the rotated basis), out = grid[code] * 2^(sf-127) * scale.
+ * Gives the tensor the reference kernel stores (mxfp4_triton.py:168-174); used by the
+ * pseudo-quantizing wrapper mxfp4_forward_kernel_wrapper (mxfp4_triton.py:177-220).
+ */
+int quartet_dequant(const uint8_t* codes, const uint8_t* sf, int64_t rows, int64_t cols, float scale, void* out,
+                    int out_dtype, quartet_stream_t stream);
+
+/* Host helpers for the blocked scale layout (`to_blocked`, benchmark_mxfp4.ipynb:1015-1016). */
+int64_t quartet_sf_offset(int64_t row, int64_t kblock, int64_t padded_kblocks);
+int64_t quartet_sf_bytes(int64_t rows, int64_t cols);
+
+/*
+ * Reads and clears the device-side fault word of the current device (synchronises the
+ * device).  Non-zero means a kernel gave up on a bounded wait (bits 0-7: which wait).
+ */
+int quartet_device_status(int32_t* status);
+
+const char* quartet_last_error_string(void);
+int quartet_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* QUARTET_B200_H */

@@ -1,0 +1,389 @@
+// Block-scaled MXFP4 GEMM for sm_100a:  D[M,N] = alpha * A[M,K] . B[N,K]^T
+//
+//   A, B    packed e2m1 (two per byte), K-major, row pitch K/2 bytes
+//   SFA/SFB E8M0 scales, one per 32 K-elements, in 512-byte blocks of 128 rows x 4 scales
+//   D       bf16 or fp32, row-major; optional fused "mask, then rotate back by the 32-point
+//           Hadamard" epilogue (the straight-through backward of the forward quantizer).
+//
+// Structure (one CTA per SM, persistent over 128 x BN output tiles, 192 threads):
+//   warp 0      TMA producer: per K-stage (256 elements) two tensor copies (A, B; 128B swizzle)
+//               and the stage's scale blocks as plain bulk copies, all signalling one mbarrier
+//   warp 1      allocates TMEM, copies scale blocks shared->tensor memory (tcgen05.cp) and issues
+//               tcgen05.mma.kind::mxf4.block_scale (K = 64 per instruction, fp32 accumulators in
+//               TMEM); tcgen05.commit releases the stage / publishes the accumulator
+//   warps 2-5   epilogue: tcgen05.ld one accumulator row x 32 columns per thread (= exactly one
+//               Hadamard group), scale, optional mask + un-rotation, convert, store
+// Every wait is bounded; a wait that gives up records itself in the fault word and the CTA
+// winds down (frees its TMEM) instead of hanging.
+#include "common.cuh"
+#include "quant_math.cuh"
+
+namespace quartet {
+
+constexpr int BM = 128;
+constexpr int BK_BYTES = 128;   // 256 e2m1 elements per stage along K
+constexpr int GEMM_THREADS = 192;
+
+template <int BN>
+struct GemmCfg {
+    static constexpr int STAGES = BN == 256 ? 4 : 6;
+    static constexpr int ACC_STAGES = BN == 256 ? 1 : 2;
+    static constexpr int A_BYTES = BM * BK_BYTES;           // 16 KB
+    static constexpr int B_BYTES = BN * BK_BYTES;           // 16 / 32 KB
+    static constexpr int SFA_BYTES = 1024;                  // 2 K-chunks x 512 B
+    static constexpr int SFB_BYTES = (BN / 128) * 1024;
+    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES + SFA_BYTES + SFB_BYTES;
+    static constexpr int SF_COLS = 8 + 2 * (BN / 32);       // SFA 2 x 4, SFB 2 x BN/32 columns
+    static constexpr int ACC_COL0 = 0;
+    static constexpr int SF_COL0 = ACC_STAGES * BN;         // two alternating scale buffers follow
+    static constexpr int TMEM_COLS = 512;
+    static constexpr int SMEM = STAGES * STAGE_BYTES + 256 + 1024;
+    static_assert(SF_COL0 + 2 * SF_COLS <= TMEM_COLS, "tensor memory budget");
+};
+
+struct GemmParams {
+    const uint8_t* a_sf;
+    const uint8_t* b_sf;
+    int M, N, K;
+    int k_chunks;            // K / 128
+    int m_tiles, n_tiles;
+    float alpha;
+    const uint8_t* mask;     // [M, N/8] or NULL
+    float had_scale;
+    void* d;
+    int d_f32;
+};
+
+// ---------------------------------------------------------------------------
+// tcgen05 wrappers
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ void tmem_alloc(uint32_t* dst_smem, uint32_t ncols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(dst_smem)), "r"(ncols)
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+                 : "memory");
+}
+// 32 rows x 16 bytes of shared memory -> 4 TMEM columns, replicated into all four lane quadrants
+__device__ __forceinline__ void tc_cp_sf(uint32_t taddr, uint64_t sdesc) {
+    asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(sdesc) : "memory");
+}
+__device__ __forceinline__ void tc_mma_mxf4(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                            uint32_t sfa_tmem, uint32_t sfb_tmem, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::mxf4.block_scale.block32 [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
+        :
+        : "r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(sfa_tmem), "r"(sfb_tmem)
+        : "memory");
+}
+__device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor, K-major operand, 128-byte swizzle: rows are 128 B apart,
+// groups of 8 rows 1024 B apart.
+__device__ __forceinline__ uint64_t make_desc_sw128(uint32_t saddr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((saddr & 0x3FFFFu) >> 4);       // start address
+    d |= (uint64_t)0 << 16;                          // leading byte offset (unused for swizzled K-major)
+    d |= (uint64_t)(1024 >> 4) << 32;                // stride byte offset
+    d |= (uint64_t)1 << 46;                          // descriptor version (sm_100)
+    d |= (uint64_t)2 << 61;                          // SWIZZLE_128B
+    return d;
+}
+// Descriptor for one 512-byte scale block: 32 rows x 16 B, no swizzle, 8-row groups 128 B apart.
+__device__ __forceinline__ uint64_t make_desc_sf(uint32_t saddr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((saddr & 0x3FFFFu) >> 4);
+    d |= (uint64_t)(128 >> 4) << 32;
+    d |= (uint64_t)1 << 46;
+    return d;
+}
+// Instruction descriptor, kind::mxf4, E2M1 x E2M1, UE8M0 scales, both operands K-major, M = 128.
+__device__ __forceinline__ uint32_t make_idesc(int n, uint32_t sf_id) {
+    uint32_t d = 0;
+    d |= sf_id << 4;                    // B scale id (byte pair within the 32-bit scale column)
+    d |= 1u << 7;                       // A format E2M1
+    d |= 1u << 10;                      // B format E2M1
+    d |= (uint32_t)(n >> 3) << 17;      // N
+    d |= 1u << 23;                      // scale format UE8M0
+    d |= (uint32_t)(BM >> 4) << 24;     // M
+    d |= sf_id << 29;                   // A scale id
+    return d;
+}
+
+// Bounded wait on wall-clock time (2 s), for the pipeline barriers.
+__device__ __forceinline__ bool gemm_wait(uint64_t* bar, uint32_t parity, int32_t who, volatile int* dead) {
+    if (*dead) return false;
+    uint64_t t0 = 0;
+    for (uint32_t i = 0;; ++i) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((i & 1023u) == 1023u) {
+            uint64_t now;
+            asm volatile("mov.u64 %0, %globaltimer;" : "=l"(now));
+            if (t0 == 0) t0 = now;
+            if (now - t0 > 2000000000ull || *dead) break;
+        }
+    }
+    atomicOr(&g_status, who | 0x100);
+    *dead = 1;
+    return false;
+}
+
+template <int BN>
+__global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_mxfp4_kernel(const __grid_constant__ CUtensorMap tm_a,
+                                                                    const __grid_constant__ CUtensorMap tm_b,
+                                                                    const GemmParams p) {
+    using C = GemmCfg<BN>;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t* s_a = smem;
+    uint8_t* s_b = s_a + C::STAGES * C::A_BYTES;
+    uint8_t* s_sfa = s_b + C::STAGES * C::B_BYTES;
+    uint8_t* s_sfb = s_sfa + C::STAGES * C::SFA_BYTES;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(s_sfb + C::STAGES * C::SFB_BYTES);
+    uint64_t* full = bars;
+    uint64_t* empty = full + C::STAGES;
+    uint64_t* acc_full = empty + C::STAGES;
+    uint64_t* acc_empty = acc_full + C::ACC_STAGES;
+    uint32_t* s_tmem = reinterpret_cast<uint32_t*>(acc_empty + C::ACC_STAGES);
+    volatile int* dead = reinterpret_cast<volatile int*>(s_tmem + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < C::STAGES; ++i) {
+            mbar_init(&full[i], 1);
+            mbar_init(&empty[i], 1);
+        }
+        for (int i = 0; i < C::ACC_STAGES; ++i) {
+            mbar_init(&acc_full[i], 1);
+            mbar_init(&acc_empty[i], 4);
+        }
+        *dead = 0;
+        fence_mbar_init();
+        prefetch_tmap(&tm_a);
+        prefetch_tmap(&tm_b);
+    }
+    if (warp == 1) {
+        tmem_alloc(s_tmem, C::TMEM_COLS);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *s_tmem;
+
+    const int n_tiles_total = p.m_tiles * p.n_tiles;
+    const int k_stages = (p.k_chunks + 1) >> 1;
+    const int64_t sf_blocks_per_rowblock = p.k_chunks;  // K/128 scale blocks per 128 rows
+
+    if (warp == 0) {
+        // ------------------------------ TMA producer ------------------------------
+        if (lane == 0) {
+            uint32_t it = 0;
+            for (int tile = blockIdx.x; tile < n_tiles_total && !*dead; tile += gridDim.x) {
+                const int m_blk = tile % p.m_tiles, n_blk = tile / p.m_tiles;
+                const int m0 = m_blk * BM, n0 = n_blk * BN;
+                const int n_rowblocks = min(BN / 128, (p.N - n0) / 128);
+                for (int ks = 0; ks < k_stages; ++ks, ++it) {
+                    const int s = it % C::STAGES;
+                    const uint32_t ph = (it / C::STAGES) & 1;
+                    if (!gemm_wait(&empty[s], ph ^ 1, WAIT_GEMM_EMPTY, dead)) break;
+                    const int nch = min(2, p.k_chunks - 2 * ks);
+                    mbar_arrive_expect_tx(&full[s], C::A_BYTES + C::B_BYTES + nch * 512 * (1 + n_rowblocks));
+                    tma_load_2d(s_a + s * C::A_BYTES, &tm_a, ks * BK_BYTES, m0, &full[s]);
+                    tma_load_2d(s_b + s * C::B_BYTES, &tm_b, ks * BK_BYTES, n0, &full[s]);
+                    bulk_load(s_sfa + s * C::SFA_BYTES, p.a_sf + ((int64_t)m_blk * sf_blocks_per_rowblock + 2 * ks) * 512,
+                              nch * 512, &full[s]);
+                    for (int rb = 0; rb < n_rowblocks; ++rb)
+                        bulk_load(s_sfb + s * C::SFB_BYTES + rb * 1024,
+                                  p.b_sf + ((int64_t)(n0 / 128 + rb) * sf_blocks_per_rowblock + 2 * ks) * 512, nch * 512,
+                                  &full[s]);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------ MMA issuer ------------------------------
+        if (lane == 0) {
+            uint32_t it = 0, acc_it = 0;
+            for (int tile = blockIdx.x; tile < n_tiles_total && !*dead; tile += gridDim.x, ++acc_it) {
+                const int n0 = (tile / p.m_tiles) * BN;
+                const int n_rowblocks = min(BN / 128, (p.N - n0) / 128);
+                const int as = acc_it % C::ACC_STAGES;
+                const uint32_t aph = (acc_it / C::ACC_STAGES) & 1;
+                if (!gemm_wait(&acc_empty[as], aph ^ 1, WAIT_GEMM_ACC_EMPTY, dead)) break;
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + C::ACC_COL0 + as * BN;
+                for (int ks = 0; ks < k_stages; ++ks, ++it) {
+                    const int s = it % C::STAGES;
+                    const uint32_t ph = (it / C::STAGES) & 1;
+                    if (!gemm_wait(&full[s], ph, WAIT_GEMM_FULL, dead)) break;
+                    tc_fence_after();
+                    const int nch = min(2, p.k_chunks - 2 * ks);
+                    const uint32_t sf_tmem = tmem_base + C::SF_COL0 + (it & 1) * C::SF_COLS;
+                    const uint32_t sa = smem_u32(s_a + s * C::A_BYTES);
+                    const uint32_t sb = smem_u32(s_b + s * C::B_BYTES);
+                    const uint32_t ssfa = smem_u32(s_sfa + s * C::SFA_BYTES);
+                    const uint32_t ssfb = smem_u32(s_sfb + s * C::SFB_BYTES);
+                    for (int c = 0; c < nch; ++c) {
+                        tc_cp_sf(sf_tmem + c * 4, make_desc_sf(ssfa + c * 512));
+                        for (int rb = 0; rb < n_rowblocks; ++rb)
+                            tc_cp_sf(sf_tmem + 8 + c * (BN / 32) + rb * 4, make_desc_sf(ssfb + rb * 1024 + c * 512));
+                    }
+                    const uint64_t adesc = make_desc_sw128(sa), bdesc = make_desc_sw128(sb);
+                    for (int c = 0; c < nch; ++c) {
+#pragma unroll
+                        for (int j = 0; j < 2; ++j) {
+                            const uint32_t koff = (uint32_t)((c * 2 + j) * 32) >> 4;  // 64 elements = 32 bytes
+                            const uint32_t sfid = (uint32_t)j * 2u;
+                            tc_mma_mxf4(d_tmem, adesc + koff, bdesc + koff, make_idesc(BN, sfid),
+                                        (sf_tmem + c * 4) | (sfid << 30), (sf_tmem + 8 + c * (BN / 32)) | (sfid << 30),
+                                        (ks | c | j) != 0);
+                        }
+                    }
+                    tc_commit(&empty[s]);  // frees the stage once the MMAs above have read it
+                }
+                tc_commit(&acc_full[as]);  // accumulator complete
+            }
+        }
+    } else {
+        // ------------------------------ epilogue ------------------------------
+        const int q = warp & 3;  // TMEM lane quadrant this warp may read
+        uint32_t acc_it = 0;
+        for (int tile = blockIdx.x; tile < n_tiles_total && !*dead; tile += gridDim.x, ++acc_it) {
+            const int m_blk = tile % p.m_tiles, n_blk = tile / p.m_tiles;
+            const int n0 = n_blk * BN;
+            const int as = acc_it % C::ACC_STAGES;
+            const uint32_t aph = (acc_it / C::ACC_STAGES) & 1;
+            if (!gemm_wait(&acc_full[as], aph, WAIT_GEMM_ACC_FULL, dead)) break;
+            tc_fence_after();
+            const int64_t row = (int64_t)m_blk * BM + q * 32 + lane;
+            const int n_chunks = min(BN, p.N - n0) / 32;
+            for (int ch = 0; ch < n_chunks; ++ch) {
+                uint32_t r[32];
+                tc_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + C::ACC_COL0 + as * BN + ch * 32, r);
+                tc_wait_ld();
+                float v[32];
+#pragma unroll
+                for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) * p.alpha;
+                const int64_t col = (int64_t)n0 + ch * 32;
+                if (p.mask) {
+                    const uint32_t m = *reinterpret_cast<const uint32_t*>(p.mask + row * (p.N >> 3) + (col >> 3));
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) v[i] = ((m >> i) & 1u) ? v[i] : 0.f;
+                    wht32(v);
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) v[i] *= p.had_scale;
+                }
+                if (p.d_f32) {
+                    float4* o = reinterpret_cast<float4*>(static_cast<float*>(p.d) + row * p.N + col);
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) o[j] = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+                } else {
+                    uint4* o = reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.d) + row * p.N + col);
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        uint32_t w[4];
+#pragma unroll
+                        for (int k = 0; k < 4; ++k) {
+                            __nv_bfloat162 t = __floats2bfloat162_rn(v[8 * j + 2 * k], v[8 * j + 2 * k + 1]);
+                            w[k] = *reinterpret_cast<uint32_t*>(&t);
+                        }
+                        o[j] = make_uint4(w[0], w[1], w[2], w[3]);
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&acc_empty[as]);
+        }
+    }
+
+    // ------------------------------ wind-down ------------------------------
+    __syncwarp();
+    tc_fence_before();
+    __syncthreads();
+    if (*dead) {
+        // a wait gave up: give copies still in flight time to land before shared memory is released
+        for (int i = 0; i < 2000; ++i) __nanosleep(1000);
+    }
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, C::TMEM_COLS);
+    }
+}
+
+template <int BN>
+static int launch_gemm(const uint8_t* a, const uint8_t* b, const GemmParams& p0, cudaStream_t stream) {
+    using C = GemmCfg<BN>;
+    GemmParams p = p0;
+    p.n_tiles = (p.N + BN - 1) / BN;
+    CUtensorMap tm_a, tm_b;
+    int rc = make_tmap_2d(&tm_a, a, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, p.K / 2, p.M, p.K / 2, BK_BYTES, BM, 3);
+    if (rc) return rc;
+    rc = make_tmap_2d(&tm_b, b, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, p.K / 2, p.N, p.K / 2, BK_BYTES, p.N < BN ? p.N : BN, 3);
+    if (rc) return rc;
+    auto kern = gemm_mxfp4_kernel<BN>;
+    rc = check_cuda(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM), "cudaFuncSetAttribute");
+    if (rc) return rc;
+    int dev = 0, sms = 0;
+    if ((rc = check_cuda(cudaGetDevice(&dev), "cudaGetDevice"))) return rc;
+    if ((rc = check_cuda(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev), "cudaDeviceGetAttribute"))) return rc;
+    const int tiles = p.m_tiles * p.n_tiles;
+    const int grid = tiles < sms ? tiles : sms;
+    kern<<<grid, GEMM_THREADS, C::SMEM, stream>>>(tm_a, tm_b, p);
+    return check_cuda(cudaGetLastError(), "gemm launch");
+}
+
+QUARTET_DEFINE_STATUS_READER(status_gemm)
+
+}  // namespace quartet
+
+using namespace quartet;
+
+extern "C" __attribute__((visibility("default"))) int quartet_gemm_mxfp4_tn(const uint8_t* a, const uint8_t* a_sf, const uint8_t* b, const uint8_t* b_sf,
+                                     int64_t M, int64_t N, int64_t K, float alpha, const uint8_t* mask,
+                                     float had_scale, void* d, int d_dtype, quartet_stream_t stream) {
+    if (!a || !a_sf || !b || !b_sf || !d) return fail(QUARTET_E_NULL, "a, a_sf, b, b_sf and d must be non-NULL");
+    if (M < 128 || N < 128 || K < 128 || M % 128 || N % 128 || K % 128)
+        return fail(QUARTET_E_SHAPE, "M, N, K must be multiples of 128 (got %lld, %lld, %lld)", (long long)M, (long long)N,
+                    (long long)K);
+    if (M > (1 << 30) || N > (1 << 30) || K > (1 << 30)) return fail(QUARTET_E_SHAPE, "extent too large");
+    if (!aligned16(a) || !aligned16(b) || !aligned16(a_sf) || !aligned16(b_sf) || !aligned16(d) ||
+        (mask && (reinterpret_cast<uintptr_t>(mask) & 3)))
+        return fail(QUARTET_E_ALIGN, "operands must be 16-byte aligned (mask: 4-byte)");
+    if (d_dtype != QUARTET_BF16 && d_dtype != QUARTET_F32) return fail(QUARTET_E_ARG, "d_dtype must be 0 or 1");
+    int rc = check_device();
+    if (rc) return rc;
+    GemmParams p{};
+    p.a_sf = a_sf, p.b_sf = b_sf;
+    p.M = (int)M, p.N = (int)N, p.K = (int)K;
+    p.k_chunks = (int)(K / 128);
+    p.m_tiles = (int)(M / BM);
+    p.alpha = alpha, p.mask = mask, p.had_scale = had_scale;
+    p.d = d, p.d_f32 = d_dtype == QUARTET_F32;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (N % 256 == 0 || N > 1024) return launch_gemm<256>(a, b, p, s);
+    return launch_gemm<128>(a, b, p, s);
+}

@@ -1,0 +1,216 @@
+// Per-group arithmetic shared by the quantizer kernels: 32-point Walsh-Hadamard in
+// registers, Philox4x32-10, the three rounding rules and e2m1 packing.
+// One thread owns one group of 32 values throughout.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <stdint.h>
+
+namespace quartet {
+
+// Unnormalised Sylvester-ordered WHT: w_j = sum_i x_i (-1)^popc(i & j).
+__device__ __forceinline__ void wht32(float (&v)[32]) {
+#pragma unroll
+    for (int s = 1; s < 32; s <<= 1) {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+            if ((i & s) == 0) {
+                float a = v[i], b = v[i + s];
+                v[i] = a + b;
+                v[i + s] = a - b;
+            }
+        }
+    }
+}
+
+__device__ __forceinline__ void unpack_bf16x8(const uint4& q, float* out) {
+    const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        out[2 * i] = __uint_as_float(w[i] << 16);
+        out[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
+    }
+}
+
+// ---------------------------------------------------------------------------
+// Philox4x32-10 (Salmon et al. 2011), word order as in triton/language/random.py:13-41.
+// ---------------------------------------------------------------------------
+struct Philox4 {
+    uint32_t w[4];
+};
+__device__ __forceinline__ Philox4 philox4x32_10(uint32_t c0, uint32_t c1, uint32_t c2, uint32_t c3, uint32_t k0,
+                                                 uint32_t k1) {
+    constexpr uint32_t KA = 0x9E3779B9u, KB = 0xBB67AE85u, RA = 0xD2511F53u, RB = 0xCD9E8D57u;
+#pragma unroll
+    for (int r = 0; r < 10; ++r) {
+        const uint32_t hb = __umulhi(RB, c2), lb = RB * c2;
+        const uint32_t ha = __umulhi(RA, c0), la = RA * c0;
+        c0 = hb ^ c1 ^ k0;
+        c2 = ha ^ c3 ^ k1;
+        c1 = lb;
+        c3 = la;
+        k0 += KA;
+        k1 += KB;
+    }
+    return Philox4{{c0, c1, c2, c3}};
+}
+// tl.rand(seed, offset): first Philox word -> [0, 1)  (triton/language/random.py:127-157)
+__device__ __forceinline__ float tl_rand(uint64_t seed, uint32_t offset) {
+    const Philox4 p = philox4x32_10(offset, 0u, 0u, 0u, (uint32_t)seed, (uint32_t)(seed >> 32));
+    int32_t x = (int32_t)p.w[0];
+    x = x < 0 ? -x - 1 : x;
+    return __int2float_rn(x) * 4.6566127342e-10f;
+}
+
+// ---------------------------------------------------------------------------
+// scales
+// ---------------------------------------------------------------------------
+// floor(log2(s)) + 127 for a positive normal float = its exponent field.
+__device__ __forceinline__ int exp_field(float s) { return (int)((__float_as_uint(s) >> 23) & 0xFFu); }
+__device__ __forceinline__ float pow2_biased(int b) { return __uint_as_float((uint32_t)b << 23); }  // 2^(b-127), 1<=b<=254
+
+// ---------------------------------------------------------------------------
+// rounding
+// ---------------------------------------------------------------------------
+// Eight values -> eight e2m1 codes in one word (element 0 in the lowest nibble) with the hardware
+// round-to-nearest-even conversion.  Differs from the reference's strict-`>` ladder
+// (mxfp4_triton.py:131-159) only when |v| is EXACTLY 0.75, 1.75 or 3.5.
+__device__ __forceinline__ uint32_t cvt_e2m1x8_rn(const float* v) {
+    uint32_t r;
+    asm("{\n\t.reg .b8 b0, b1, b2, b3;\n\t.reg .b16 h0, h1;\n\t"
+        "cvt.rn.satfinite.e2m1x2.f32 b0, %2, %1;\n\t"
+        "cvt.rn.satfinite.e2m1x2.f32 b1, %4, %3;\n\t"
+        "cvt.rn.satfinite.e2m1x2.f32 b2, %6, %5;\n\t"
+        "cvt.rn.satfinite.e2m1x2.f32 b3, %8, %7;\n\t"
+        "mov.b16 h0, {b0, b1};\n\tmov.b16 h1, {b2, b3};\n\tmov.b32 %0, {h0, h1};\n\t}"
+        : "=r"(r)
+        : "f"(v[0]), "f"(v[1]), "f"(v[2]), "f"(v[3]), "f"(v[4]), "f"(v[5]), "f"(v[6]), "f"(v[7]));
+    return r;
+}
+
+// One byte (two codes) -> two floats, exact.
+__device__ __forceinline__ float2 e2m1x2_to_float2(uint32_t byte) {
+    uint32_t h2;
+    asm("{\n\t.reg .b8 lo, hi;\n\t.reg .b16 t;\n\tcvt.u16.u32 t, %1;\n\tmov.b16 {lo, hi}, t;\n\t"
+        "cvt.rn.f16x2.e2m1x2 %0, lo;\n\t}"
+        : "=r"(h2)
+        : "r"(byte));
+    return __half22float2(*reinterpret_cast<__half2*>(&h2));
+}
+
+// Reference ladder index for |v| with strict `>` (ties toward the smaller magnitude).
+__device__ __forceinline__ int rtn_index_exact(float a) {
+    return (a > 0.25f) + (a > 0.75f) + (a > 1.25f) + (a > 1.75f) + (a > 2.5f) + (a > 3.5f) + (a > 5.0f);
+}
+
+// Reference stochastic rounding: bracket by strict `>`, p = (a - lo) / (hi - lo), up iff u < p.
+__device__ __forceinline__ int sr_index_exact(float a, float u) {
+    const int lo = (a > 0.5f) + (a > 1.0f) + (a > 1.5f) + (a > 2.0f) + (a > 3.0f) + (a > 4.0f);
+    const float glo = lo < 4 ? 0.5f * lo : (lo == 4 ? 2.0f : (lo == 5 ? 3.0f : 4.0f));
+    const float inv_step = lo < 4 ? 2.0f : (lo < 6 ? 1.0f : 0.5f);
+    const float p = (a - glo) * inv_step;  // exact: the step is a power of two
+    return lo + ((u < p) ? 1 : 0);
+}
+
+// Own-stream stochastic rounding of a = |v| in [0, 6] with an 8-bit dither `d8` already placed as
+// (d8 << 8 | 0x80): values below 1 are shifted by +1 so the grid step is bit 22 of the pattern
+// everywhere; adding ((d8 << 14) + (1 << 13)) and dropping 22 bits rounds up with probability
+// round(256 frac) / 256.
+__device__ __forceinline__ int sr_index_dither(float a, uint32_t d8_placed) {
+    const bool small = a < 1.0f;
+    const float t = small ? a + 1.0f : a;
+    const uint32_t bits = __float_as_uint(t) + d8_placed * 64u;
+    return (int)(bits >> 22) - (small ? 254 : 252);
+}
+
+
+__device__ __forceinline__ uint32_t spread_sign_bits(uint32_t s8) {
+    // bit i of s8 -> bit 4i+3 (the sign bit of nibble i)
+    uint32_t r = 0;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) r |= ((s8 >> i) & 1u) << (4 * i + 3);
+    return r;
+}
+
+// ---------------------------------------------------------------------------
+// Backward (absmax-scaled) quantization of one rotated group.
+//   w      unnormalised WHT output; the rotated values are h * w
+//   g      index of the group in the OUTPUT tensor (row-major over [out_rows, out_cols/32]);
+//          counter of the own Philox stream
+//   flat   index of the group's first element in the output tensor, for the caller-supplied noise
+//          tensor and the tl.rand-compatible stream
+//   flip   sign-vector of the rotation (H @ diag(s)) spread onto nibble sign bits
+// Scale byte: E8M0 = floor(log2 amax) - 2 + 127 (the reference's extra 1/0.75 goes into the GEMM
+// alpha, mxfp4_triton.py:60).
+// ---------------------------------------------------------------------------
+template <int ROUND>
+__device__ __forceinline__ void absmax_quantize_group(const float (&w)[32], float h, uint64_t g, int64_t flat,
+                                                      bool noise_valid, uint64_t seed, uint64_t offset,
+                                                      const float* noise, const uint32_t (&flip)[4],
+                                                      uint32_t (&words)[4], int& e8m0) {
+    float amax = 0.f;
+#pragma unroll
+    for (int i = 0; i < 32; ++i) amax = fmaxf(amax, fabsf(w[i]));
+    amax *= h;  // max |h w| = h max|w|  (h > 0, rounding is monotone)
+    const int eb = exp_field(amax);
+    e8m0 = max(eb - 2, 0);
+    if (ROUND == 1 /* QUARTET_ROUND_SR_PHILOX */) {
+        const bool zero = eb < 3;
+        const float c = zero ? 0.f : (0.75f * h) * pow2_biased(254 - e8m0);
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+            const uint64_t ctr = 2 * g + j;
+            const Philox4 r = philox4x32_10((uint32_t)ctr, (uint32_t)(ctr >> 32), (uint32_t)offset,
+                                            (uint32_t)(offset >> 32), (uint32_t)seed, (uint32_t)(seed >> 32));
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+                uint32_t acc = 0;
+#pragma unroll
+                for (int t = 0; t < 8; ++t) {
+                    const int i = 16 * j + 8 * half + t;
+                    const float v = w[i] * c;
+                    // (dither byte << 8) | 0x80
+                    const uint32_t d = __byte_perm(r.w[2 * half + (t >> 2)], 0x80u, 0x5504 | ((t & 3) << 4));
+                    const int idx = sr_index_dither(fabsf(v), d);
+                    acc |= ((uint32_t)idx | ((v > 0.f) ? 0u : 8u)) << (4 * t);
+                }
+                words[2 * j + half] = acc ^ flip[2 * j + half];
+            }
+        }
+    } else {
+        // reference-exact arithmetic: shared = fl(2^e / 0.75), v = xh / shared (IEEE division)
+        float shared;
+        if (eb >= 3)
+            shared = pow2_biased(eb - 2) * 1.33333337306976318359375f;
+        else if (eb == 0)
+            shared = 0.f;
+        else
+            shared = ldexpf(1.33333337306976318359375f, eb - 129);
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            uint32_t acc = 0;
+#pragma unroll
+            for (int t = 0; t < 8; ++t) {
+                const int i = 8 * q + t;
+                const float v = __fdiv_rn(w[i] * h, shared);
+                const float a = fabsf(v);
+                int idx;
+                if (ROUND == 0 /* QUARTET_ROUND_NEAREST */) {
+                    idx = rtn_index_exact(a);
+                } else {
+                    float u;
+                    if (ROUND == 2 /* QUARTET_ROUND_SR_NOISE */)
+                        u = noise_valid ? __ldg(noise + flat + i) : 0.f;
+                    else
+                        u = tl_rand(seed, (uint32_t)(flat + i));
+                    idx = sr_index_exact(a, u);
+                }
+                acc |= ((uint32_t)idx | ((v > 0.f) ? 0u : 8u)) << (4 * t);
+            }
+            words[q] = acc ^ flip[q];
+        }
+    }
+}
+
+}  // namespace quartet

@@ -1,0 +1,249 @@
+// Transposing backward quantizers: groups of 32 run along the ROWS of the source, the result is
+// the quantized TRANSPOSE (codes_t [cols, rows/2], scales logical [cols, rows/32]).
+//
+//   SRC_BF16 / SRC_F32  source is a dense tensor        -> `g_quantizer(e.T.contiguous())`
+//                                                           (backward.py:81 of the reference)
+//   SRC_MXFP4           source is codes + blocked scales -> `g_quantizer(w.T.contiguous())`,
+//                                                           `g_quantizer(x.T.contiguous())`
+//                                                           (backward.py:73,82)
+//
+// One CTA handles a 128 x 128 source tile.  TMA loads it into shared memory; a thread owns two
+// adjacent source columns over 32 consecutive source rows (= two output groups), reads them
+// column-wise from shared memory (conflict-free: a warp reads 32 neighbouring words of one row),
+// rotates/rounds/packs in registers and stages 2 x 16 B of codes; the transposed 128 x 64 B code
+// tile and the tile's single 512-byte scale block leave through TMA / bulk stores.
+#include "common.cuh"
+#include "quant_math.cuh"
+
+namespace quartet {
+
+enum { SRC_BF16 = 0, SRC_F32 = 1, SRC_MXFP4 = 2 };
+
+struct TileTParams {
+    int64_t rows, cols;       // source extents
+    const uint8_t* sf_in;     // SRC_MXFP4: blocked scales of the source
+    int64_t sf_in_blocks_per_rowblock;
+    float in_scale;
+    uint8_t* sf_t;            // blocked scales of the transposed result
+    int64_t sf_t_blocks_per_rowblock;  // pad4(rows/32) / 4
+    float had_scale;
+    uint32_t signs;
+    const uint32_t* signs_dev;
+    uint64_t seed, offset;
+    const float* noise;
+};
+
+constexpr int TT = 128, TT_THREADS = 256;
+
+template <int SRC>
+__host__ __device__ constexpr int tile_in_bytes() {
+    return SRC == SRC_BF16 ? TT * TT * 2 : (SRC == SRC_F32 ? TT * TT * 4 : TT * TT / 2 + 512);
+}
+template <int SRC>
+constexpr int tile_smem_bytes() {
+    return tile_in_bytes<SRC>() + TT * 64 + 512 + 64 + 1024;
+}
+
+template <int SRC, int ROUND>
+__global__ void __launch_bounds__(TT_THREADS, 2) quant_tile_t_kernel(const __grid_constant__ CUtensorMap tm_in,
+                                                                    const __grid_constant__ CUtensorMap tm_out,
+                                                                    const TileTParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    constexpr int IN_BYTES = tile_in_bytes<SRC>();
+    constexpr int BOX_BYTES = TT * 128;
+    uint8_t* s_in = smem;
+    uint8_t* s_codes = smem + IN_BYTES;   // [128 out rows][64 B]
+    uint8_t* s_sf = s_codes + TT * 64;    // 512 B
+    uint64_t* bar = reinterpret_cast<uint64_t*>(s_sf + 512);
+
+    const int tid = threadIdx.x;
+    const int col0 = blockIdx.x * TT;              // source column of the tile = output row
+    const int row0 = blockIdx.y * TT;              // source row of the tile    = output column
+
+    if (tid == 0) {
+        mbar_init(bar, 1);
+        fence_mbar_init();
+    }
+    __syncthreads();
+    if (tid == 0) {
+        if (SRC == SRC_MXFP4) {
+            mbar_arrive_expect_tx(bar, TT * 64 + 512);
+            tma_load_2d(s_in, &tm_in, col0 / 2, row0, bar);
+            const uint8_t* sf_src = p.sf_in + ((int64_t)blockIdx.y * p.sf_in_blocks_per_rowblock + blockIdx.x) * 512;
+            bulk_load(s_in + TT * 64, sf_src, 512, bar);
+        } else {
+            constexpr int NBOX = SRC == SRC_F32 ? 4 : 2;
+            mbar_arrive_expect_tx(bar, NBOX * BOX_BYTES);
+#pragma unroll
+            for (int b = 0; b < NBOX; ++b)
+                tma_load_2d(s_in + b * BOX_BYTES, &tm_in, col0 + b * (SRC == SRC_F32 ? 32 : 64), row0, bar);
+        }
+    }
+
+    const uint32_t signs = p.signs_dev ? __ldg(p.signs_dev) : p.signs;
+    uint32_t flip[4];
+#pragma unroll
+    for (int q = 0; q < 4; ++q) flip[q] = spread_sign_bits((signs >> (8 * q)) & 0xFFu);
+
+    mbar_wait(bar, 0, WAIT_QUANT_LOAD);
+
+    const int cp = tid & 63;   // source column pair within the tile
+    const int rg = tid >> 6;   // group of 32 source rows within the tile
+    float a[32], b[32];        // columns 2cp and 2cp+1 over rows rg*32 .. rg*32+31
+
+    if (SRC == SRC_BF16) {
+        const uint8_t* base = s_in + (cp >> 5) * BOX_BYTES;
+        const int chunk = (cp & 31) >> 2, word = cp & 3;
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+            const int r = rg * 32 + i;
+            const uint32_t v = *reinterpret_cast<const uint32_t*>(base + r * 128 + ((chunk ^ (r & 7)) << 4) + word * 4);
+            a[i] = __uint_as_float(v << 16);
+            b[i] = __uint_as_float(v & 0xFFFF0000u);
+        }
+    } else if (SRC == SRC_F32) {
+        const uint8_t* base = s_in + (cp >> 4) * BOX_BYTES;
+        const int chunk = (cp & 15) >> 1, half = cp & 1;
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+            const int r = rg * 32 + i;
+            const float2 v = *reinterpret_cast<const float2*>(base + r * 128 + ((chunk ^ (r & 7)) << 4) + half * 8);
+            a[i] = v.x;
+            b[i] = v.y;
+        }
+    } else {
+        const uint8_t* s_sfin = s_in + TT * 64;
+        const int kb = cp >> 4;  // source scale block (32 source columns) of this column pair
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+            const int r = rg * 32 + i;
+            const uint32_t byte = s_in[r * 64 + cp];
+            const uint32_t sfb = s_sfin[i * 16 + rg * 4 + kb];  // (r % 32) * 16 + (r / 32) * 4 + kb
+            const float sc = __uint_as_float(sfb << 23) * p.in_scale;
+            const float2 f = e2m1x2_to_float2(byte);
+            a[i] = f.x * sc;
+            b[i] = f.y * sc;
+        }
+    }
+
+    wht32(a);
+    wht32(b);
+
+    const int64_t out_kb = (int64_t)(row0 >> 5) + rg;           // scale block along the output row
+    const int64_t groups_per_out_row = p.rows >> 5;
+    uint32_t words[4];
+    int e8m0;
+#pragma unroll
+    for (int c = 0; c < 2; ++c) {
+        const int oc = 2 * cp + c;                               // output row within the tile
+        const int64_t orow = (int64_t)col0 + oc;
+        const uint64_t g = (uint64_t)orow * (uint64_t)groups_per_out_row + (uint64_t)out_kb;
+        const int64_t flat = orow * p.rows + out_kb * 32;
+        if (c == 0)
+            absmax_quantize_group<ROUND>(a, p.had_scale, g, flat, true, p.seed, p.offset, p.noise, flip, words, e8m0);
+        else
+            absmax_quantize_group<ROUND>(b, p.had_scale, g, flat, true, p.seed, p.offset, p.noise, flip, words, e8m0);
+        *reinterpret_cast<uint4*>(s_codes + oc * 64 + rg * 16) = make_uint4(words[0], words[1], words[2], words[3]);
+        s_sf[(oc & 31) * 16 + (oc >> 5) * 4 + rg] = (uint8_t)e8m0;
+    }
+
+    fence_proxy_async_smem();
+    __syncthreads();
+    if (tid == 0) {
+        tma_store_2d(&tm_out, row0 / 2, col0, s_codes);
+        uint8_t* sf_dst = p.sf_t + ((int64_t)blockIdx.x * p.sf_t_blocks_per_rowblock + blockIdx.y) * 512;
+        bulk_store(sf_dst, s_sf, 512);
+        bulk_commit();
+        bulk_wait_read0();
+    }
+}
+
+template <int SRC, int ROUND>
+static int launch_tile_t(const void* src, const TileTParams& p, uint8_t* codes_t, cudaStream_t stream) {
+    CUtensorMap tm_in, tm_out;
+    int rc;
+    if (SRC == SRC_F32)
+        rc = make_tmap_2d(&tm_in, src, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, p.cols, p.rows, p.cols * 4, 32, TT, 3);
+    else if (SRC == SRC_BF16)
+        rc = make_tmap_2d(&tm_in, src, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, p.cols, p.rows, p.cols * 2, 64, TT, 3);
+    else
+        rc = make_tmap_2d(&tm_in, src, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, p.cols / 2, p.rows, p.cols / 2, 64, TT, 0);
+    if (rc) return rc;
+    rc = make_tmap_2d(&tm_out, codes_t, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, p.rows / 2, p.cols, p.rows / 2, 64, TT, 0);
+    if (rc) return rc;
+    auto kern = quant_tile_t_kernel<SRC, ROUND>;
+    constexpr int smem = tile_smem_bytes<SRC>();
+    rc = check_cuda(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem), "cudaFuncSetAttribute");
+    if (rc) return rc;
+    dim3 grid((unsigned)(p.cols / TT), (unsigned)(p.rows / TT));
+    kern<<<grid, TT_THREADS, smem, stream>>>(tm_in, tm_out, p);
+    return check_cuda(cudaGetLastError(), "quant_tile_t launch");
+}
+
+static int validate_tile_t(const void* src, int64_t rows, int64_t cols, const void* codes_t, const void* sf_t, int rounding,
+                           const float* noise) {
+    if (!src || !codes_t || !sf_t) return fail(QUARTET_E_NULL, "source, codes_t and sf_t must be non-NULL");
+    if (rows < 128 || cols < 128 || rows % 128 != 0 || cols % 128 != 0)
+        return fail(QUARTET_E_SHAPE, "need rows and cols to be multiples of 128 (got %lld x %lld)", (long long)rows, (long long)cols);
+    if (rows > 0x7FFFFFFF || cols > 0x7FFFFFFF || rows / 128 > 65535)
+        return fail(QUARTET_E_SHAPE, "extent too large (rows <= 8388480)");
+    if (!aligned16(src) || !aligned16(codes_t) || !aligned16(sf_t)) return fail(QUARTET_E_ALIGN, "pointers must be 16-byte aligned");
+    if (rounding < 0 || rounding > 3) return fail(QUARTET_E_ARG, "rounding must be 0..3");
+    if (rounding == QUARTET_ROUND_SR_NOISE && !noise) return fail(QUARTET_E_NULL, "noise tensor required for rounding mode 2");
+    if (rounding == QUARTET_ROUND_SR_TLRAND && rows * cols > 0x7FFFFFFFLL)
+        return fail(QUARTET_E_SHAPE, "rounding mode 3 indexes elements with 31 bits");
+    return check_device();
+}
+
+template <int SRC>
+static int dispatch_round(const void* src, const TileTParams& p, uint8_t* codes_t, int rounding, cudaStream_t s) {
+    switch (rounding) {
+        case 0: return launch_tile_t<SRC, 0>(src, p, codes_t, s);
+        case 1: return launch_tile_t<SRC, 1>(src, p, codes_t, s);
+        case 2: return launch_tile_t<SRC, 2>(src, p, codes_t, s);
+        default: return launch_tile_t<SRC, 3>(src, p, codes_t, s);
+    }
+}
+
+QUARTET_DEFINE_STATUS_READER(status_tile_t)
+
+}  // namespace quartet
+
+using namespace quartet;
+
+extern "C" __attribute__((visibility("default"))) int quartet_quant_bwd_t(const void* x, int x_dtype, int64_t rows, int64_t cols, float had_scale,
+                                   uint32_t signs, const uint32_t* signs_dev, int rounding, uint64_t seed,
+                                   uint64_t offset, const float* noise, uint8_t* codes_t, uint8_t* sf_t,
+                                   quartet_stream_t stream) {
+    int rc = validate_tile_t(x, rows, cols, codes_t, sf_t, rounding, noise);
+    if (rc) return rc;
+    if (x_dtype != QUARTET_BF16 && x_dtype != QUARTET_F32) return fail(QUARTET_E_ARG, "x_dtype must be 0 (bf16) or 1 (f32)");
+    TileTParams p{};
+    p.rows = rows, p.cols = cols;
+    p.sf_t = sf_t, p.sf_t_blocks_per_rowblock = ((rows / 32 + 3) / 4);
+    p.had_scale = had_scale, p.signs = signs, p.signs_dev = signs_dev;
+    p.seed = seed, p.offset = offset, p.noise = noise;
+    p.in_scale = 1.f;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    return x_dtype == QUARTET_F32 ? dispatch_round<SRC_F32>(x, p, codes_t, rounding, s)
+                                  : dispatch_round<SRC_BF16>(x, p, codes_t, rounding, s);
+}
+
+extern "C" __attribute__((visibility("default"))) int quartet_requant_t(const uint8_t* codes, const uint8_t* sf, int64_t rows, int64_t cols, float in_scale,
+                                 float had_scale, uint32_t signs, const uint32_t* signs_dev, int rounding,
+                                 uint64_t seed, uint64_t offset, const float* noise, uint8_t* codes_t, uint8_t* sf_t,
+                                 quartet_stream_t stream) {
+    int rc = validate_tile_t(codes, rows, cols, codes_t, sf_t, rounding, noise);
+    if (rc) return rc;
+    if (!sf) return fail(QUARTET_E_NULL, "sf must be non-NULL");
+    if (!aligned16(sf)) return fail(QUARTET_E_ALIGN, "sf must be 16-byte aligned");
+    TileTParams p{};
+    p.rows = rows, p.cols = cols;
+    p.sf_in = sf, p.sf_in_blocks_per_rowblock = ((cols / 32 + 3) / 4);
+    p.in_scale = in_scale;
+    p.sf_t = sf_t, p.sf_t_blocks_per_rowblock = ((rows / 32 + 3) / 4);
+    p.had_scale = had_scale, p.signs = signs, p.signs_dev = signs_dev;
+    p.seed = seed, p.offset = offset, p.noise = noise;
+    return dispatch_round<SRC_MXFP4>(codes, p, codes_t, rounding, static_cast<cudaStream_t>(stream));
+}

@@ -1,0 +1,166 @@
+"""Tensor-level wrappers over the C ABI.  torch supplies device memory and the
+current stream; all arithmetic happens in libquartet_b200.so."""
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+
+from . import _lib
+
+BF16, F32 = 0, 1
+ROUND_NEAREST, ROUND_SR_PHILOX, ROUND_SR_NOISE, ROUND_SR_TLRAND = 0, 1, 2, 3
+QUEST_GAUSSIAN_SCALE = 2.92247856 / 6.0
+HAD_SCALE_BF16 = 0.1767578125  # bf16(32 ** -0.5)
+HAD_SCALE_F32 = 0.17677669529663687
+SR_OPERAND_SCALE = 4.0 / 3.0  # each absmax-quantized operand carries this factor outside its scale bytes
+
+
+def _dt(t: torch.Tensor) -> int:
+    if t.dtype == torch.bfloat16:
+        return BF16
+    if t.dtype == torch.float32:
+        return F32
+    raise ValueError(f"dtype {t.dtype} not supported (bf16 or fp32)")
+
+
+def _out_dt(dtype: torch.dtype) -> int:
+    if dtype == torch.bfloat16:
+        return BF16
+    if dtype == torch.float32:
+        return F32
+    raise ValueError(f"output dtype {dtype} not supported (bf16 or fp32)")
+
+
+def _ptr(t):
+    return None if t is None else C.c_void_p(t.data_ptr())
+
+
+def _stream():
+    return C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _need_cuda(*ts):
+    for t in ts:
+        if t is not None and not t.is_cuda:
+            raise ValueError("tensors must live on a CUDA device")
+        if t is not None and not t.is_contiguous():
+            raise ValueError("tensors must be contiguous")
+
+
+def sf_bytes(rows: int, cols: int) -> int:
+    return ((rows + 127) // 128 * 128) * ((cols // 32 + 3) // 4 * 4)
+
+
+def quant_fwd(x, had_scale=HAD_SCALE_BF16, gaussian_scale=QUEST_GAUSSIAN_SCALE, return_mask=True):
+    """[rows, cols] -> (codes [rows, cols/2] u8, sf blocked u8, mask [rows, cols/8] u8 | None)."""
+    _need_cuda(x)
+    rows, cols = x.shape
+    codes = torch.empty(rows, cols // 2, dtype=torch.uint8, device=x.device)
+    sf = torch.empty(sf_bytes(rows, cols), dtype=torch.uint8, device=x.device)
+    mask = torch.empty(rows, cols // 8, dtype=torch.uint8, device=x.device) if return_mask else None
+    with torch.cuda.device(x.device):
+        rc = _lib.load().quartet_quant_fwd(_ptr(x), _dt(x), rows, cols, had_scale, gaussian_scale, _ptr(codes), _ptr(sf),
+                                           _ptr(mask), _stream())
+    _lib.check(rc, "quartet_quant_fwd")
+    return codes, sf, mask
+
+
+def _sr_args(signs, signs_dev, seed, offset, noise):
+    return (int(signs) & 0xFFFFFFFF, _ptr(signs_dev)), (int(seed) & (2**64 - 1), int(offset) & (2**64 - 1), _ptr(noise))
+
+
+def quant_bwd(x, had_scale=HAD_SCALE_BF16, signs=0, signs_dev=None, rounding=ROUND_SR_PHILOX, seed=0, offset=0, noise=None):
+    """Row-wise backward quantizer: (codes [rows, cols/2], sf blocked); value = grid * 2^(sf-127) * 4/3."""
+    _need_cuda(x, noise, signs_dev)
+    rows, cols = x.shape
+    codes = torch.empty(rows, cols // 2, dtype=torch.uint8, device=x.device)
+    sf = torch.empty(sf_bytes(rows, cols), dtype=torch.uint8, device=x.device)
+    (s, sd), (sd_, off, nz) = _sr_args(signs, signs_dev, seed, offset, noise)
+    with torch.cuda.device(x.device):
+        rc = _lib.load().quartet_quant_bwd(_ptr(x), _dt(x), rows, cols, had_scale, s, sd, rounding, sd_, off, nz, _ptr(codes),
+                                           _ptr(sf), _stream())
+    _lib.check(rc, "quartet_quant_bwd")
+    return codes, sf
+
+
+def quant_bwd_t(x, had_scale=HAD_SCALE_BF16, signs=0, signs_dev=None, rounding=ROUND_SR_PHILOX, seed=0, offset=0, noise=None):
+    """Backward quantizer of x^T: (codes_t [cols, rows/2], sf_t blocked for [cols, rows/32])."""
+    _need_cuda(x, noise, signs_dev)
+    rows, cols = x.shape
+    codes_t = torch.empty(cols, rows // 2, dtype=torch.uint8, device=x.device)
+    sf_t = torch.empty(sf_bytes(cols, rows), dtype=torch.uint8, device=x.device)
+    (s, sd), (sd_, off, nz) = _sr_args(signs, signs_dev, seed, offset, noise)
+    with torch.cuda.device(x.device):
+        rc = _lib.load().quartet_quant_bwd_t(_ptr(x), _dt(x), rows, cols, had_scale, s, sd, rounding, sd_, off, nz,
+                                             _ptr(codes_t), _ptr(sf_t), _stream())
+    _lib.check(rc, "quartet_quant_bwd_t")
+    return codes_t, sf_t
+
+
+def requant_t(codes, sf, in_scale=1.0, had_scale=HAD_SCALE_BF16, signs=0, signs_dev=None, rounding=ROUND_SR_PHILOX, seed=0,
+              offset=0, noise=None):
+    """MXFP4 [rows, cols] -> backward-quantized transpose (codes_t [cols, rows/2], sf_t)."""
+    _need_cuda(codes, sf, noise, signs_dev)
+    rows, cols = codes.shape[0], codes.shape[1] * 2
+    codes_t = torch.empty(cols, rows // 2, dtype=torch.uint8, device=codes.device)
+    sf_t = torch.empty(sf_bytes(cols, rows), dtype=torch.uint8, device=codes.device)
+    (s, sd), (sd_, off, nz) = _sr_args(signs, signs_dev, seed, offset, noise)
+    with torch.cuda.device(codes.device):
+        rc = _lib.load().quartet_requant_t(_ptr(codes), _ptr(sf), rows, cols, in_scale, had_scale, s, sd, rounding, sd_, off,
+                                           nz, _ptr(codes_t), _ptr(sf_t), _stream())
+    _lib.check(rc, "quartet_requant_t")
+    return codes_t, sf_t
+
+
+def gemm_mxfp4_tn(a, a_sf, b, b_sf, alpha=1.0, mask=None, had_scale=HAD_SCALE_BF16, out_dtype=torch.bfloat16, out=None):
+    """D[M,N] = alpha * A[M,K] . B[N,K]^T on packed e2m1 operands with blocked E8M0 scales."""
+    _need_cuda(a, a_sf, b, b_sf, mask, out)
+    M, K = a.shape[0], a.shape[1] * 2
+    N = b.shape[0]
+    if b.shape[1] * 2 != K:
+        raise ValueError(f"contraction extents differ: {K} vs {b.shape[1] * 2}")
+    if out is None:
+        out = torch.empty(M, N, dtype=out_dtype, device=a.device)
+    with torch.cuda.device(a.device):
+        rc = _lib.load().quartet_gemm_mxfp4_tn(_ptr(a), _ptr(a_sf), _ptr(b), _ptr(b_sf), M, N, K, alpha, _ptr(mask), had_scale,
+                                               _ptr(out), _out_dt(out.dtype), _stream())
+    _lib.check(rc, "quartet_gemm_mxfp4_tn")
+    return out
+
+
+def unrotate_mask(g, mask=None, had_scale=HAD_SCALE_BF16, out_dtype=None):
+    """((g * mask).view(-1, 32) @ H^T).view_as(g)"""
+    _need_cuda(g, mask)
+    out = torch.empty_like(g, dtype=out_dtype or g.dtype)
+    cols = g.shape[-1]
+    rows = g.numel() // cols
+    with torch.cuda.device(g.device):
+        rc = _lib.load().quartet_unrotate_mask(_ptr(g), _dt(g), _ptr(mask), rows, cols, had_scale, _ptr(out), _out_dt(out.dtype),
+                                               _stream())
+    _lib.check(rc, "quartet_unrotate_mask")
+    return out
+
+
+def dequant(codes, sf, scale=1.0, dtype=torch.float32):
+    """codes [rows, cols/2] + blocked sf -> [rows, cols] values grid * 2^(sf-127) * scale."""
+    _need_cuda(codes, sf)
+    rows, cols = codes.shape[0], codes.shape[1] * 2
+    out = torch.empty(rows, cols, dtype=dtype, device=codes.device)
+    with torch.cuda.device(codes.device):
+        rc = _lib.load().quartet_dequant(_ptr(codes), _ptr(sf), rows, cols, scale, _ptr(out), _out_dt(dtype), _stream())
+    _lib.check(rc, "quartet_dequant")
+    return out
+
+
+def device_status() -> int:
+    """Fault word of the current device (0 = no kernel ever gave up on a bounded wait); clears it."""
+    st = C.c_int32(0)
+    _lib.check(_lib.load().quartet_device_status(C.byref(st)), "quartet_device_status")
+    return st.value
+
+
+def unpack_mask(mask_u8: torch.Tensor) -> torch.Tensor:
+    """[rows, cols/8] bit-packed (LSB first) -> bool [rows, cols]  (benchmark_mxfp4.ipynb:975-979 `_unpack_mask`)."""
+    bits = torch.arange(8, device=mask_u8.device, dtype=torch.uint8)
+    return ((mask_u8.unsqueeze(-1) >> bits) & 1).bool().reshape(*mask_u8.shape[:-1], mask_u8.shape[-1] * 8)
