@@ -1,0 +1,328 @@
+"""Benchmark of the MXFP4 quantized-linear path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Workload ("llama7b_linears_16384tok"): the four linear layers of a 7B Llama block
+(QKV 4096->12288, O 4096->4096, gate/up 4096->22016, down 11008->4096), forward + dgrad + wgrad,
+16384 tokens per GPU, bf16 activations ~N(0,1), fp32 master weights ~N(0,0.02), bf16 grad-outputs
+~N(0,1e-3); synthetic, seeded.  One step = all four layers once, through
+quartet_b200.quantization.QuantizedLinear (forward + backward).  Token rows are sharded over the
+GPUs (weak scaling: 16384 tokens on every GPU); the per-GPU weight-gradient partials are averaged
+with an NCCL reduce-scatter inside the step.  Metric: model FLOP/s = 6*M*N*K per layer, summed over
+layers and GPUs.
+
+`--impl reference` times the reference's own pseudo-quantized arithmetic for the same layers on the
+host CPU (the torch-fp32 restatement in oracle/ref_math.py, which is pinned bit-exactly to the
+reference kernel) on a bounded token sample.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+LAYERS = [("qkv", 4096, 12288), ("o", 4096, 4096), ("gate_up", 4096, 22016), ("down", 11008, 4096)]
+TOKENS = 16384
+CPU_SAMPLE_TOKENS = 512
+WORKLOAD = "llama7b_linears_16384tok"
+METRIC = "quantized_linear_fwd_bwd_tflops"
+
+
+def layer_flops(m):
+    return sum(6.0 * m * k * n for _, k, n in LAYERS)
+
+
+# ----------------------------------------------------------------------------------------------
+# CPU arm (the reference's arithmetic on host cores)
+# ----------------------------------------------------------------------------------------------
+def cpu_arm(steps, warmup, tokens=CPU_SAMPLE_TOKENS):
+    import torch
+
+    from oracle import ref_math as rm
+
+    cores = len(os.sched_getaffinity(0))
+    torch.set_num_threads(cores)
+    gen = torch.Generator().manual_seed(0)
+    data = []
+    for _, k, n in LAYERS:
+        x = torch.randn(tokens, k, generator=gen).bfloat16().float()
+        w = (torch.randn(n, k, generator=gen) * 0.02).bfloat16().float()
+        e = (torch.randn(tokens, n, generator=gen) * 1e-3).bfloat16().float()
+        data.append((x, w, e))
+    times = []
+    for it in range(warmup + steps):
+        t0 = time.perf_counter()
+        for x, w, e in data:
+            rm.cpu_layer_fwd_bwd(x, w, e, seed=it)
+        if it >= warmup:
+            times.append(time.perf_counter() - t0)
+    dt = sum(times) / len(times)
+    return layer_flops(tokens) / dt / 1e12, dt, cores, f"{tokens} of {TOKENS} tokens per layer, all four layers, fp32 torch ops"
+
+
+# ----------------------------------------------------------------------------------------------
+# clocks
+# ----------------------------------------------------------------------------------------------
+class ClockSampler:
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.rows, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100",
+                                          "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm = sorted(int(r[1]) for r in self.rows if len(r) >= 9 and r[1].isdigit())
+        reasons = set()
+        for r in self.rows:
+            if len(r) >= 9:
+                for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[5:9]):
+                    if v.lower().startswith("active"):
+                        reasons.add(name)
+        smax = next((int(r[2]) for r in self.rows if len(r) >= 9 and r[2].isdigit()), None)
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": smax, "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# ----------------------------------------------------------------------------------------------
+# GPU arm
+# ----------------------------------------------------------------------------------------------
+def gpu_arm(args):
+    import torch
+    import torch.distributed as dist
+
+    import __graft_entry__ as entry
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    if rank == 0:
+        entry.build()
+    if world > 1:
+        dist.barrier()
+    from quartet_b200 import ops
+    from quartet_b200.quantization import BACKWARD_SCHEMES, QUANTIZER_CLASSES, QuantizedLinear
+    from quartet_b200.shard import WgradReduceScatter
+
+    # ---- model + data (seeded; weights identical on every rank, activations differ per rank) ----
+    gw = torch.Generator(device="cpu").manual_seed(0)
+    layers, xs, es, xs_host, es_host = [], [], [], [], []
+    for _, k, n in LAYERS:
+        lin = QuantizedLinear(
+            k, n, bias=False,
+            weight_quantizer=QUANTIZER_CLASSES["QuestMXFP4Quantizer"](),
+            activation_quantizer=QUANTIZER_CLASSES["QuestMXFP4Quantizer"](),
+            gradient_quantizer=QUANTIZER_CLASSES["AlbertTsengQuantizer"](stochastic=True, rerotate="signs"),
+            backward_scheme=BACKWARD_SCHEMES["Q(E)Q(Wt)t_Q(Et)Q(Xt)t"](),
+        )
+        with torch.no_grad():
+            lin.weight.copy_(torch.randn(n, k, generator=gw) * 0.02)
+        layers.append(lin.to(dev))
+    torch.manual_seed(1000 + rank)
+    for _, k, n in LAYERS:
+        xh = torch.randn(TOKENS, k, dtype=torch.bfloat16).pin_memory()
+        eh = (torch.randn(TOKENS, n) * 1e-3).to(torch.bfloat16).pin_memory()
+        xs_host.append(xh), es_host.append(eh)
+        xs.append(xh.to(dev).requires_grad_(True)), es.append(eh.to(dev))
+    reducer = WgradReduceScatter(world) if world > 1 else None
+
+    # ---- count launches of this library's kernels and time them per kind ----
+    counts = {"n": 0}
+    timing = {"on": False, "rec": []}
+
+    def wrap(name, fn, work):
+        def inner(*a, **k):
+            counts["n"] += 1
+            if not timing["on"]:
+                return fn(*a, **k)
+            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s.record()
+            out = fn(*a, **k)
+            e.record()
+            timing["rec"].append((name, s, e, work(*a, **k)))
+            return out
+
+        return inner
+
+    def q_bytes(per_elem, with_mask=0.0):
+        return lambda x, *a, **k: ("bytes", x.numel() * (x.element_size() + per_elem + (with_mask if k.get("return_mask", True) else 0)))
+
+    real = {n: getattr(ops, n) for n in ("quant_fwd", "quant_bwd", "quant_bwd_t", "requant_t", "gemm_mxfp4_tn")}
+    ops.quant_fwd = wrap("quant_fwd", real["quant_fwd"], q_bytes(0.53125, 0.125))
+    ops.quant_bwd = wrap("quant_bwd", real["quant_bwd"], lambda x, *a, **k: ("bytes", x.numel() * (x.element_size() + 0.53125)))
+    ops.quant_bwd_t = wrap("quant_bwd_t", real["quant_bwd_t"], lambda x, *a, **k: ("bytes", x.numel() * (x.element_size() + 0.53125)))
+    ops.requant_t = wrap("requant_t", real["requant_t"], lambda c, *a, **k: ("bytes", c.numel() * 2 * 1.0625))
+    ops.gemm_mxfp4_tn = wrap("gemm", real["gemm_mxfp4_tn"],
+                             lambda a_, asf, b_, *r, **k: ("flops", 2.0 * a_.shape[0] * b_.shape[0] * a_.shape[1] * 2))
+
+    def step(from_host=False):
+        sums = []
+        for i, lin in enumerate(layers):
+            if from_host:
+                xs[i].data.copy_(xs_host[i], non_blocking=True)
+                es[i].copy_(es_host[i], non_blocking=True)
+            xs[i].grad = None
+            lin.weight.grad = None
+            y = lin(xs[i])
+            y.backward(es[i])
+            if reducer is not None:
+                reducer.submit(lin.weight.grad)
+            if from_host:
+                sums.append(torch.stack([y.float().sum(), xs[i].grad.float().sum(), lin.weight.grad.float().sum()]))
+        if reducer is not None:
+            reducer.wait()
+        if from_host:
+            return torch.stack(sums).cpu()  # the step's result read back to the host
+        return None
+
+    def timed(n_steps, from_host):
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        for _ in range(n_steps):
+            step(from_host)
+        e.record()
+        torch.cuda.synchronize()
+        ms = torch.tensor([s.elapsed_time(e)], device=dev)
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+            dist.barrier()
+        return ms.item()
+
+    for _ in range(args.warmup):
+        step()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    counts["n"] = 0
+    total_ms = timed(args.steps, False)
+    launches = counts["n"]
+    clocks = sampler.stop() if rank == 0 else None
+
+    step(True)
+    e2e_ms = timed(args.steps, True)
+
+    # ---- per-kernel timing (live, CUDA events on the launching stream, outside the headline region) ----
+    timing["on"] = True
+    for _ in range(max(2, min(args.steps, 5))):
+        step()
+    torch.cuda.synchronize()
+    timing["on"] = False
+    agg = {}
+    for name, s, e, (kind, work) in timing["rec"]:
+        a = agg.setdefault(name, {"ms": 0.0, "work": 0.0, "kind": kind, "n": 0})
+        a["ms"] += s.elapsed_time(e)
+        a["work"] += work
+        a["n"] += 1
+    status = ops.device_status()
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+    peaks = {}
+    try:
+        peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+    except OSError:
+        pass
+    hbm_peak = peaks.get("hbm_gbs", 6650.0)
+    bf16_peak = peaks.get("bf16_tflops_sustained", 1400.0)
+    peak_note = "measured" if peaks else "fallback"
+    ms_per_step = total_ms / args.steps
+    flops = layer_flops(TOKENS) * world
+    value = flops / (ms_per_step * 1e-3) / 1e12
+    g = agg["gemm"]
+    gemm_tflops = g["work"] / (g["ms"] * 1e-3) / 1e12
+    qn = [k for k in agg if k != "gemm"]
+    q_ms = sum(agg[k]["ms"] for k in qn)
+    q_gbs = sum(agg[k]["work"] for k in qn) / (q_ms * 1e-3) / 1e9
+    h2d = sum(t.numel() * t.element_size() for t in xs_host + es_host)
+    cpu_v, cpu_dt, cores, sample = cpu_arm(1, 0)
+    out = {
+        "metric": METRIC, "value": round(value, 2), "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": round(ms_per_step, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "mxfp4",
+        "data": "synthetic",
+        "config": {"workload": WORKLOAD, "tokens_per_gpu": TOKENS, "layers": [[n_, k, n] for n_, k, n in LAYERS],
+                   "activations": "bf16", "weights": "fp32 master", "parallelism": f"dp{world} token-row shards + NCCL reduce-scatter of wgrad",
+                   "l2": "inputs larger than L2 (>= 134 MB per operand, 3.9 GB per step)"},
+        "e2e": {"value": round(flops / (e2e_ms / args.steps * 1e-3) / 1e12, 2), "unit": "TFLOP/s", "h2d_bytes_per_step": h2d,
+                "d2h_bytes_per_step": len(LAYERS) * 3 * 4, "ms_per_step": round(e2e_ms / args.steps, 3),
+                "note": "activations and grad-outputs copied from pinned host memory every step; weights stay resident; per-layer checksums of y, dx, dw read back"},
+        "gpu_launches": launches,
+        "clocks": clocks,
+        "roofline": {"bound": "tensor", "kernel": "gemm_mxfp4_kernel", "achieved": round(gemm_tflops, 1), "peak": round(4 * bf16_peak, 1),
+                     "unit": "TFLOP/s", "frac": round(gemm_tflops / (4 * bf16_peak), 4), "traffic": None,
+                     "peak_note": f"4 x {peak_note} sustained bf16 cuBLAS rate (MXFP4:bf16 dense ratio of the tensor cores)",
+                     "launches": g["n"], "avg_ms": round(g["ms"] / g["n"], 4)},
+        "roofline_quantizers": {"bound": "hbm", "achieved": round(q_gbs, 1), "peak": hbm_peak, "unit": "GB/s", "frac": round(q_gbs / hbm_peak, 4),
+                                "peak_note": f"{peak_note} copy bandwidth",
+                                "per_kernel": {k: {"GB/s": round(agg[k]["work"] / (agg[k]["ms"] * 1e-3) / 1e9, 1), "launches": agg[k]["n"],
+                                                   "ms": round(agg[k]["ms"], 3)} for k in qn}},
+        "time_share": {k: round(agg[k]["ms"] / sum(a["ms"] for a in agg.values()), 4) for k in agg},
+        "cpu_baseline": {"value": round(cpu_v, 5), "unit": "TFLOP/s", "cores": cores, "kind": "port", "sample": sample,
+                         "seconds": round(cpu_dt, 2)},
+        "device_fault_word": status,
+    }
+    print(json.dumps(out), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    if args.impl == "reference":
+        if int(os.environ.get("RANK", "0")) != 0:
+            return
+        steps = min(args.steps, 5)
+        v, dt, cores, sample = cpu_arm(steps, min(args.warmup, 1))
+        print(json.dumps({
+            "impl": "reference", "metric": METRIC, "value": round(v, 5), "unit": "TFLOP/s", "n_gpus": args.gpus, "steps": steps,
+            "warmup": min(args.warmup, 1), "ms_per_step": round(dt * 1e3, 2), "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": WORKLOAD, "tokens_per_gpu": TOKENS, "layers": [[n_, k, n] for n_, k, n in LAYERS]},
+            "cpu_baseline": {"value": round(v, 5), "unit": "TFLOP/s", "cores": cores, "kind": "port", "sample": sample},
+            "e2e": {"value": round(v, 5), "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        }), flush=True)
+        return
+    gpu_arm(args)
+
+
+if __name__ == "__main__":
+    main()

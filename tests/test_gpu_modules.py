@@ -1,0 +1,158 @@
+"""The host-side mirror of the reference's module interface, on the GPU: the pseudo-quantizing
+wrapper, the quantizer modules and QuantizedLinear (fused and composed) against the golden vectors
+and the oracle."""
+import os
+import random
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import ref_math as rm
+from tests import helpers as H
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def Q():
+    import __graft_entry__ as entry
+
+    entry.build()
+    import quartet_b200.quantization as q
+
+    return q
+
+
+def _production_linear(Q, k, n, **gkw):
+    return Q.QuantizedLinear(
+        k, n, bias=False,
+        weight_quantizer=Q.QUANTIZER_CLASSES["QuestMXFP4Quantizer"](),
+        activation_quantizer=Q.QUANTIZER_CLASSES["QuestMXFP4Quantizer"](),
+        gradient_quantizer=Q.QUANTIZER_CLASSES["AlbertTsengQuantizer"](**gkw),
+        backward_scheme=Q.BACKWARD_SCHEMES["Q(E)Q(Wt)t_Q(Et)Q(Xt)t"](),
+    ).cuda()
+
+
+def test_kernel_wrapper_matches_reference_kernel(Q, golden_dir):
+    g = np.load(os.path.join(golden_dir, "quantizer_kernel.npz"))
+    h = rm.hadamard32().bfloat16().cuda()
+    hb = (rm.hadamard32() * rm.signs_to_diag(int(g["signs"]))[None, :]).bfloat16().cuda()
+    for name in ("gauss", "grad", "student"):
+        x = torch.from_numpy(g[name + "_x"]).bfloat16().cuda()
+        out, mask = Q.mxfp4_forward_kernel_wrapper(x, h, return_clip_mask=True, stochastic_round=False, quest=True,
+                                                   gaussian_scale=2.92247856 / 6.0)
+        assert out.dtype == x.dtype and out.shape == x.shape and mask.dtype == torch.bool
+        assert bool((out.float().cpu() == torch.from_numpy(g[name + "_quest_out"])).all())
+        assert bool((mask.cpu() == torch.from_numpy(g[name + "_quest_mask"])).all())
+        random.seed(1234)  # the generator drew its seed from this state
+        out, _ = Q.mxfp4_forward_kernel_wrapper(x, hb, stochastic_round=True, quest=False)
+        ref = torch.from_numpy(g[name + "_sr_out"]).bfloat16().float()  # q * fl(2^e * 4/3) rounds when stored as bf16
+        assert bool((out.float().cpu() == ref).all())
+
+
+def test_fused_linear_against_golden(Q, golden_dir):
+    from quartet_b200 import ops
+
+    g = np.load(os.path.join(golden_dir, "linear_fwd_bwd.npz"))
+    x, w, e = (torch.from_numpy(g[k]) for k in "xwe")
+    lin = _production_linear(Q, w.shape[1], w.shape[0], stochastic=True, rerotate=None)
+    assert list(lin.state_dict().keys()) == ["weight"]
+    with torch.no_grad():
+        lin.weight.copy_(w)
+    lin.weight.data = lin.weight.data.bfloat16()  # bf16 operands -> bf16-rounded rotation, as in the golden run
+    gq = lin.backward_scheme.g_quantizer
+    gq.hadamard_matrix = (rm.hadamard32() * rm.signs_to_diag(int(g["signs"]))[None, :]).bfloat16()
+    gq.sr_rounding = ops.ROUND_SR_TLRAND
+    xd = x.bfloat16().cuda().requires_grad_(True)
+    random.seed(0)  # golden: the four seeds are the first four draws after random.seed(0)
+    y = lin(xd)
+    y.backward(e.bfloat16().cuda())
+    for name, got in (("y", y), ("dx", xd.grad), ("dw", lin.weight.grad)):
+        ref = torch.from_numpy(g[name])
+        err = ((got.float().cpu() - ref).norm() / ref.norm()).item()
+        print(name, err)
+        assert err < 1e-2  # bf16 outputs: 2^-9 rounding
+    assert ops.device_status() == 0
+
+
+def test_fused_linear_matches_composed_modules(Q):
+    """Fused real-MXFP4 path == composing the quantizer modules the way the reference does."""
+    from quartet_b200 import ops
+
+    torch.manual_seed(0)
+    lin = _production_linear(Q, 256, 384, stochastic=False, rerotate="signs")
+    x = torch.randn(2, 128, 256, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    e = (torch.randn(2, 128, 384, device="cuda") * 1e-3).bfloat16()
+    with torch.autocast("cuda", dtype=torch.bfloat16):
+        y = lin(x)
+    y.backward(e)
+    assert y.dtype == torch.bfloat16 and x.grad.dtype == torch.bfloat16 and lin.weight.grad.dtype == torch.float32
+    # composed: quantizer modules + F.linear, masks and un-rotation through the autograd of the quantizers
+    aq, wq = Q.QuestMXFP4Quantizer(), Q.QuestMXFP4Quantizer()
+    x2 = x.detach().clone().requires_grad_(True)
+    w2 = lin.weight.detach().clone().requires_grad_(True)
+    xq, wqq = aq(x2), wq(w2)
+    y2 = torch.nn.functional.linear(xq.float(), wqq.float())
+    assert ((y.float() - y2).norm() / y2.norm()).item() < 1e-2
+    gq = Q.AlbertTsengQuantizer(stochastic=False)
+    e2 = e.reshape(-1, 384)
+    gx = torch.nn.functional.linear(gq(e2).float(), gq(wqq.detach().T.contiguous()).float())
+    gw = gq(e2.T.contiguous()).float() @ gq(xq.detach().reshape(-1, 256).T.contiguous()).float().T
+    xq.backward(gx.reshape(xq.shape).to(xq.dtype))
+    wqq.backward(gw.to(wqq.dtype))
+    assert ((x.grad.float() - x2.grad.float()).norm() / x2.grad.float().norm()).item() < 2e-2
+    assert ((lin.weight.grad - w2.grad).norm() / w2.grad.norm()).item() < 2e-2
+    assert ops.device_status() == 0
+
+
+def test_rerandomize_keeps_results_and_state(Q):
+    """Sign re-randomisation flips code signs of both GEMM operands alike, so gradients do not change
+    with round-to-nearest; the sign word accumulates on the device and shows up in hadamard_matrix."""
+    torch.manual_seed(1)
+    lin = _production_linear(Q, 128, 128, stochastic=False, rerotate="signs")
+    x = torch.randn(128, 128, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    e = torch.randn(128, 128, device="cuda", dtype=torch.bfloat16)
+    lin(x).backward(e)
+    g1 = x.grad.clone()
+    x.grad = None
+    lin(x).backward(e)
+    assert bool((x.grad == g1).all())
+    gq = lin.backward_scheme.g_quantizer
+    hm = gq.hadamard_matrix
+    assert hm.shape == (32, 32) and hm.dtype == torch.bfloat16
+    assert bool((hm.float().abs() == 0.1767578125).all())
+    assert gq._sign_word() != 0
+
+
+def test_other_combinations_compose_like_the_reference(Q):
+    lin = Q.QuantizedLinear(128, 256, bias=False).cuda()
+    x = torch.randn(8, 128, device="cuda", requires_grad=True)
+    lin(x).sum().backward()
+    assert x.grad is not None
+    with pytest.raises(NotImplementedError):
+        Q.QUANTIZER_CLASSES["HadamardTrustQuantizer"]()
+    with pytest.raises(NotImplementedError):
+        Q.AlbertTsengQuantizer(rerotate="O32").re_randomize(device="cuda")
+    assert len(Q.QUANTIZER_CLASSES) == 40 and set(Q.BACKWARD_SCHEMES) == {"EW_EtX", "Q(E)W_Q(Et)X", "Q(E)Q(Wt)t_Q(Et)Q(Xt)t"}
+    # un-fused scheme with an MXFP4 gradient quantizer
+    lin = Q.QuantizedLinear(128, 256, bias=False, gradient_quantizer=Q.AlbertTsengQuantizer(stochastic=True),
+                            backward_scheme=Q.BACKWARD_SCHEMES["Q(E)W_Q(Et)X"]()).cuda()
+    x = torch.randn(128, 128, device="cuda", requires_grad=True)
+    y = lin(x)
+    y.backward(torch.randn_like(y))
+    ref = torch.nn.functional.linear
+    assert x.grad.shape == x.shape and lin.weight.grad.shape == lin.weight.shape
+
+
+def test_ragged_token_count(Q):
+    """Token counts that are not a multiple of 128 are padded inside the fused path."""
+    torch.manual_seed(2)
+    lin = _production_linear(Q, 128, 256, stochastic=True, rerotate="signs")
+    x = torch.randn(3, 50, 128, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    y = lin(x)
+    assert y.shape == (3, 50, 256)
+    y.backward(torch.randn_like(y))
+    assert x.grad.shape == x.shape and torch.isfinite(x.grad.float()).all() and torch.isfinite(lin.weight.grad).all()
+    ref = torch.nn.functional.linear(x.float(), lin.weight.float())
+    assert ((y.float() - ref).norm() / ref.norm()).item() < 0.35

@@ -228,5 +228,5 @@ def test_roundtrip_property_large(ops):
     xr = ops.unrotate_mask(val, None, ops.HAD_SCALE_BF16)  # rotate back (H is symmetric, orthonormal up to bf16 rounding)
     rel = ((xr - x.float()).norm() / x.float().norm()).item()
     print("fwd quantizer relative error", rel)
-    assert 0.08 < rel < 0.16
+    assert 0.08 < rel < 0.22
     assert ops.device_status() == 0
