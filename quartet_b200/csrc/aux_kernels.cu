@@ -94,8 +94,9 @@ extern "C" __attribute__((visibility("default"))) int quartet_dequant(const uint
     if (rows < 1 || cols < 32 || cols % 32 != 0) return fail(QUARTET_E_SHAPE, "need rows >= 1 and cols a multiple of 32");
     if (!aligned16(codes) || !aligned16(out)) return fail(QUARTET_E_ALIGN, "pointers must be 16-byte aligned");
     if (out_dtype != QUARTET_BF16 && out_dtype != QUARTET_F32) return fail(QUARTET_E_ARG, "out_dtype must be 0 or 1");
-    int rc = check_device();
+    int rc = bind_context_of(codes);
     if (rc) return rc;
+    if ((rc = check_device())) return rc;
     const int64_t groups = rows * (cols / 32);
     const unsigned blocks = (unsigned)((groups + 255) / 256);
     cudaStream_t s = static_cast<cudaStream_t>(stream);
@@ -113,8 +114,9 @@ extern "C" __attribute__((visibility("default"))) int quartet_unrotate_mask(cons
     if (!aligned16(g) || !aligned16(out) || (mask && (reinterpret_cast<uintptr_t>(mask) & 3)))
         return fail(QUARTET_E_ALIGN, "g/out must be 16-byte aligned, mask 4-byte aligned");
     if ((g_dtype | out_dtype) & ~1) return fail(QUARTET_E_ARG, "dtypes must be 0 (bf16) or 1 (f32)");
-    int rc = check_device();
+    int rc = bind_context_of(g);
     if (rc) return rc;
+    if ((rc = check_device())) return rc;
     const int64_t groups = rows * (cols / 32);
     const unsigned blocks = (unsigned)((groups + 255) / 256);
     cudaStream_t s = static_cast<cudaStream_t>(stream);

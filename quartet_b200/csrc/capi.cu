@@ -23,6 +23,33 @@ int check_cuda(cudaError_t e, const char* what) {
     return fail(QUARTET_E_CUDA, "%s: %s", what, cudaGetErrorString(e));
 }
 
+// The calling thread may have no CUDA context bound yet (PyTorch's autograd worker threads bind one
+// lazily, and this library carries its own statically linked runtime): bind the primary context of
+// the device that owns `ptr` before anything that needs a current context (tensor-map encoding,
+// launches).  Cheap when a context is already current.
+int bind_context_of(const void* ptr) {
+    typedef CUresult (*GetCurFn)(CUcontext*);
+    typedef CUresult (*PtrAttrFn)(void*, CUpointer_attribute, CUdeviceptr);
+    static GetCurFn get_cur = nullptr;
+    static PtrAttrFn ptr_attr = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuCtxGetCurrent", &p, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
+            get_cur = reinterpret_cast<GetCurFn>(p);
+        if (cudaGetDriverEntryPoint("cuPointerGetAttribute", &p, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
+            ptr_attr = reinterpret_cast<PtrAttrFn>(p);
+    });
+    if (!get_cur || !ptr_attr) return fail(QUARTET_E_CUDA, "driver entry points unavailable");
+    CUcontext ctx = nullptr;
+    if (get_cur(&ctx) == CUDA_SUCCESS && ctx != nullptr) return QUARTET_OK;
+    int ordinal = -1;
+    if (ptr_attr(&ordinal, CU_POINTER_ATTRIBUTE_DEVICE_ORDINAL, reinterpret_cast<CUdeviceptr>(ptr)) != CUDA_SUCCESS || ordinal < 0)
+        return fail(QUARTET_E_CUDA, "pointer %p is not device memory", ptr);
+    return check_cuda(cudaSetDevice(ordinal), "cudaSetDevice");
+}
+
 int check_device() {
     static thread_local int cached_dev = -1;
     static thread_local int cached_ok = 0;

@@ -15,6 +15,8 @@
 //               Hadamard group), scale, optional mask + un-rotation, convert, store
 // Every wait is bounded; a wait that gives up records itself in the fault word and the CTA
 // winds down (frees its TMEM) instead of hanging.
+#include <cstdlib>
+
 #include "common.cuh"
 #include "quant_math.cuh"
 
@@ -374,8 +376,9 @@ extern "C" __attribute__((visibility("default"))) int quartet_gemm_mxfp4_tn(cons
         (mask && (reinterpret_cast<uintptr_t>(mask) & 3)))
         return fail(QUARTET_E_ALIGN, "operands must be 16-byte aligned (mask: 4-byte)");
     if (d_dtype != QUARTET_BF16 && d_dtype != QUARTET_F32) return fail(QUARTET_E_ARG, "d_dtype must be 0 or 1");
-    int rc = check_device();
+    int rc = bind_context_of(a);
     if (rc) return rc;
+    if ((rc = check_device())) return rc;
     GemmParams p{};
     p.a_sf = a_sf, p.b_sf = b_sf;
     p.M = (int)M, p.N = (int)N, p.K = (int)K;
@@ -384,6 +387,13 @@ extern "C" __attribute__((visibility("default"))) int quartet_gemm_mxfp4_tn(cons
     p.alpha = alpha, p.mask = mask, p.had_scale = had_scale;
     p.d = d, p.d_f32 = d_dtype == QUARTET_F32;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    if (N % 256 == 0 || N > 1024) return launch_gemm<256>(a, b, p, s);
+    // Tile width: 256 unless the output is narrow or not a multiple of 256.  QUARTET_GEMM_BN=128|256
+    // overrides the choice (tuning aid).
+    static const int forced_bn = [] {
+        const char* e = getenv("QUARTET_GEMM_BN");
+        return e ? atoi(e) : 0;
+    }();
+    const bool wide = forced_bn ? forced_bn == 256 : (N % 256 == 0 || N > 1024);
+    if (wide) return launch_gemm<256>(a, b, p, s);
     return launch_gemm<128>(a, b, p, s);
 }

@@ -192,6 +192,8 @@ static int validate_rows(const void* x, int x_dtype, int64_t rows, int64_t cols,
     if (rows > 0x7FFFFFFF || cols > 0x7FFFFFFF || (rows + 127) / 128 > 65535)
         return fail(QUARTET_E_SHAPE, "extent too large (rows <= 8388480)");
     if (!aligned16(x) || !aligned16(codes) || !aligned16(sf)) return fail(QUARTET_E_ALIGN, "pointers must be 16-byte aligned");
+    int rc = bind_context_of(x);
+    if (rc) return rc;
     return check_device();
 }
 

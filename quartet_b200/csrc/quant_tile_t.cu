@@ -193,6 +193,8 @@ static int validate_tile_t(const void* src, int64_t rows, int64_t cols, const vo
     if (rounding == QUARTET_ROUND_SR_NOISE && !noise) return fail(QUARTET_E_NULL, "noise tensor required for rounding mode 2");
     if (rounding == QUARTET_ROUND_SR_TLRAND && rows * cols > 0x7FFFFFFFLL)
         return fail(QUARTET_E_SHAPE, "rounding mode 3 indexes elements with 31 bits");
+    int rc = bind_context_of(src);
+    if (rc) return rc;
     return check_device();
 }
 

@@ -1,0 +1,147 @@
+"""Kernel-level micro-benchmark of the path, one kernel per run:
+
+    python -m quartet_b200.microbench --kernel quant_fwd  --rows 16384 --cols 4096 [--dtype bf16|f32]
+    python -m quartet_b200.microbench --kernel quant_bwd  --rows 16384 --cols 12288 [--rounding 1]
+    python -m quartet_b200.microbench --kernel quant_bwd_t --rows 16384 --cols 12288
+    python -m quartet_b200.microbench --kernel requant_t  --rows 16384 --cols 4096
+    python -m quartet_b200.microbench --kernel gemm --m 16384 --n 12288 --k 4096 [--fused-unrotate]
+    python -m quartet_b200.microbench --sweep            # quantize-only bandwidth sweep
+
+Timing: CUDA events on the launching stream, `--warmup` untimed launches, then `--iters` timed
+launches with a 256 MB write between launches to flush L2 (excluded from the timing).  Inputs are
+Student-t(3) with 1 % of the channels scaled x20 (the quantize-sweep distribution) unless --gauss.
+Prints one JSON line per case; quantizers report algorithmic GB/s, the GEMM TFLOP/s.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+
+import torch
+
+from . import ops
+
+BYTES_PER_ELEM = {"quant_fwd": 0.5 + 1 / 32 + 1 / 8, "quant_bwd": 0.5 + 1 / 32, "quant_bwd_t": 0.5 + 1 / 32}
+
+
+def _peaks():
+    path = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "MEASURED_PEAKS.json")
+    try:
+        return json.load(open(path))
+    except OSError:
+        return {}
+
+
+def make_input(rows, cols, dtype, gauss=False, seed=0):
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    if gauss:
+        return torch.randn(rows, cols, generator=g, device="cuda").to(dtype)
+    # Student-t(3) = N / sqrt(chi2_3 / 3)
+    z = torch.randn(rows, cols, generator=g, device="cuda")
+    c = torch.randn(3, rows, cols, generator=g, device="cuda", dtype=torch.bfloat16).float().pow(2).sum(0) / 3
+    x = z / c.sqrt()
+    ch = torch.randperm(cols, generator=g, device="cuda")[: max(1, round(0.01 * cols))]
+    x[:, ch] *= 20
+    return x.to(dtype)
+
+
+def time_kernel(fn, iters, warmup, flush=True):
+    scratch = torch.empty(256 << 20, dtype=torch.uint8, device="cuda") if flush else None
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    total = 0.0
+    best = float("inf")
+    for _ in range(iters):
+        if flush:
+            scratch.fill_(1)
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        fn()
+        e.record()
+        e.synchronize()
+        ms = s.elapsed_time(e)
+        total += ms
+        best = min(best, ms)
+    return total / iters, best
+
+
+def run_quant(kernel, rows, cols, dtype, rounding, iters, warmup, gauss):
+    esz = 2 if dtype == torch.bfloat16 else 4
+    if kernel == "requant_t":
+        x = make_input(rows, cols, torch.bfloat16, gauss)
+        codes, sf, _ = ops.quant_fwd(x)
+        del x
+        fn = lambda: ops.requant_t(codes, sf, 1.0, rounding=rounding, seed=1)  # noqa: E731
+        bytes_ = rows * cols * 2 * (0.5 + 1 / 32)
+    else:
+        x = make_input(rows, cols, dtype, gauss)
+        if kernel == "quant_fwd":
+            fn = lambda: ops.quant_fwd(x, ops.HAD_SCALE_BF16 if esz == 2 else ops.HAD_SCALE_F32)  # noqa: E731
+        elif kernel == "quant_bwd":
+            fn = lambda: ops.quant_bwd(x, rounding=rounding, seed=1)  # noqa: E731
+        else:
+            fn = lambda: ops.quant_bwd_t(x, rounding=rounding, seed=1)  # noqa: E731
+        bytes_ = rows * cols * (esz + BYTES_PER_ELEM[kernel])
+    avg, best = time_kernel(fn, iters, warmup)
+    hbm = _peaks().get("hbm_gbs", 6650.0)
+    gbs = bytes_ / (avg * 1e-3) / 1e9
+    return {"kernel": kernel, "rows": rows, "cols": cols, "dtype": "bf16" if esz == 2 else "f32", "rounding": rounding,
+            "avg_ms": round(avg, 4), "best_ms": round(best, 4), "GB/s": round(gbs, 1), "frac_of_hbm_peak": round(gbs / hbm, 4),
+            "algorithmic_bytes": int(bytes_)}
+
+
+def run_gemm(m, n, k, iters, warmup, fused, out_f32):
+    g = torch.Generator(device="cuda").manual_seed(0)
+    a = torch.randint(0, 256, (m, k // 2), generator=g, device="cuda", dtype=torch.uint8)
+    b = torch.randint(0, 256, (n, k // 2), generator=g, device="cuda", dtype=torch.uint8)
+    asf = torch.randint(118, 130, (ops.sf_bytes(m, k),), generator=g, device="cuda", dtype=torch.uint8)
+    bsf = torch.randint(118, 130, (ops.sf_bytes(n, k),), generator=g, device="cuda", dtype=torch.uint8)
+    mask = torch.randint(0, 256, (m, n // 8), generator=g, device="cuda", dtype=torch.uint8) if fused else None
+    out = torch.empty(m, n, device="cuda", dtype=torch.float32 if out_f32 else torch.bfloat16)
+    fn = lambda: ops.gemm_mxfp4_tn(a, asf, b, bsf, 16 / 9, mask=mask, out=out)  # noqa: E731
+    avg, best = time_kernel(fn, iters, warmup)
+    p = _peaks()
+    peak = 4 * p.get("bf16_tflops", 1590.0)
+    tf = 2.0 * m * n * k / (avg * 1e-3) / 1e12
+    return {"kernel": "gemm_mxfp4_tn", "m": m, "n": n, "k": k, "fused_unrotate": bool(fused), "out": "f32" if out_f32 else "bf16",
+            "avg_ms": round(avg, 4), "best_ms": round(best, 4), "TFLOP/s": round(tf, 1),
+            "frac_of_4x_bf16_burst_peak": round(tf / peak, 4)}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--kernel", default="quant_fwd", choices=["quant_fwd", "quant_bwd", "quant_bwd_t", "requant_t", "gemm"])
+    ap.add_argument("--rows", type=int, default=16384)
+    ap.add_argument("--cols", type=int, default=4096)
+    ap.add_argument("--m", type=int, default=16384)
+    ap.add_argument("--n", type=int, default=4096)
+    ap.add_argument("--k", type=int, default=4096)
+    ap.add_argument("--dtype", default="bf16", choices=["bf16", "f32"])
+    ap.add_argument("--rounding", type=int, default=ops.ROUND_SR_PHILOX)
+    ap.add_argument("--iters", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--gauss", action="store_true")
+    ap.add_argument("--fused-unrotate", action="store_true")
+    ap.add_argument("--out-f32", action="store_true")
+    ap.add_argument("--sweep", action="store_true", help="quantize-only sweep: K in {4096, 8192, 14336}, M = 4096 .. 131072")
+    args = ap.parse_args()
+    dtype = torch.bfloat16 if args.dtype == "bf16" else torch.float32
+    if args.sweep:
+        for k in (4096, 8192, 14336):
+            m = 4096
+            while m <= 131072:
+                if m * k * 2 <= 6 << 30:
+                    for kern in ("quant_fwd", "quant_bwd", "quant_bwd_t"):
+                        print(json.dumps(run_quant(kern, m, k, torch.bfloat16, args.rounding, 5, 2, False)), flush=True)
+                m *= 2
+        return
+    if args.kernel == "gemm":
+        print(json.dumps(run_gemm(args.m, args.n, args.k, args.iters, args.warmup, args.fused_unrotate, args.out_f32)))
+    else:
+        print(json.dumps(run_quant(args.kernel, args.rows, args.cols, dtype, args.rounding, args.iters, args.warmup, args.gauss)))
+
+
+if __name__ == "__main__":
+    main()
