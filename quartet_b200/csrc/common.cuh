@@ -55,6 +55,7 @@ enum : int32_t {
     WAIT_GEMM_EMPTY = 3,
     WAIT_GEMM_ACC_FULL = 4,
     WAIT_GEMM_ACC_EMPTY = 5,
+    WAIT_GEMM_SF = 6,
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
@@ -118,6 +119,7 @@ __device__ __forceinline__ void bulk_store(void* dst, const void* src, uint32_t 
 }
 __device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 __device__ __forceinline__ void bulk_wait_read0() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_read1() { asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory"); }
 __device__ __forceinline__ void bulk_wait0() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 
 __device__ __forceinline__ void prefetch_tmap(const CUtensorMap* map) {

@@ -5,14 +5,18 @@
 //   D       bf16 or fp32, row-major; optional fused "mask, then rotate back by the 32-point
 //           Hadamard" epilogue (the straight-through backward of the forward quantizer).
 //
-// Structure (one CTA per SM, persistent over 128 x BN output tiles, 192 threads):
+// Structure (one CTA per SM, persistent over 128 x BN output tiles, 320 threads):
 //   warp 0      TMA producer: per K-stage (256 elements) two tensor copies (A, B; 128B swizzle)
 //               and the stage's scale blocks as plain bulk copies, all signalling one mbarrier
-//   warp 1      allocates TMEM, copies scale blocks shared->tensor memory (tcgen05.cp) and issues
-//               tcgen05.mma.kind::mxf4.block_scale (K = 64 per instruction, fp32 accumulators in
-//               TMEM); tcgen05.commit releases the stage / publishes the accumulator
+//   warp 1      allocates TMEM and issues tcgen05.mma.kind::mxf4.block_scale back to back (K = 64
+//               per instruction, fp32 accumulators in TMEM); tcgen05.commit releases the stage /
+//               publishes the accumulator
+//   warps 6-9   scale feeders: move the stage's E8M0 bytes shared -> registers -> tensor memory
+//               (tcgen05.st), one warp per TMEM lane quadrant, so that the tensor pipe only ever
+//               sees MMAs (scale copies issued in the MMA stream serialise with them)
 //   warps 2-5   epilogue: tcgen05.ld one accumulator row x 32 columns per thread (= exactly one
-//               Hadamard group), scale, optional mask + un-rotation, convert, store
+//               Hadamard group), scale, optional mask + un-rotation, convert, stage the 32 x 32
+//               block in swizzled shared memory, TMA store
 // Every wait is bounded; a wait that gives up records itself in the fault word and the CTA
 // winds down (frees its TMEM) instead of hanging.
 #include <cstdlib>
@@ -24,7 +28,7 @@ namespace quartet {
 
 constexpr int BM = 128;
 constexpr int BK_BYTES = 128;   // 256 e2m1 elements per stage along K
-constexpr int GEMM_THREADS = 192;
+constexpr int GEMM_THREADS = 320;  // warp 0 TMA, warp 1 MMA, warps 2-5 epilogue, warps 6-9 scale feeders
 
 template <int BN>
 struct GemmCfg {
@@ -33,14 +37,19 @@ struct GemmCfg {
     static constexpr int A_BYTES = BM * BK_BYTES;           // 16 KB
     static constexpr int B_BYTES = BN * BK_BYTES;           // 16 / 32 KB
     static constexpr int SFA_BYTES = 1024;                  // 2 K-chunks x 512 B
-    static constexpr int SFB_BYTES = (BN / 128) * 1024;
+    static constexpr int SFB_BLOCKS = BN / 128;             // 128-row scale blocks a tile can touch
+    static constexpr int SFB_BYTES = SFB_BLOCKS * 1024;
     static constexpr int STAGE_BYTES = A_BYTES + B_BYTES + SFA_BYTES + SFB_BYTES;
-    static constexpr int SF_COLS = 8 + 2 * (BN / 32);       // SFA 2 x 4, SFB 2 x BN/32 columns
+    static constexpr int NSEG = BN / 32;                    // 32-row segments of B = scale columns per K-chunk
+    static constexpr int SFB_ST = NSEG <= 4 ? 4 : 8;        // columns written per tcgen05.st
+    static constexpr int SF_COLS = 8 + 2 * SFB_ST;          // SFA 2 x 4, SFB 2 x SFB_ST columns per stage
     static constexpr int ACC_COL0 = 0;
-    static constexpr int SF_COL0 = ACC_STAGES * BN;         // two alternating scale buffers follow
+    static constexpr int SF_COL0 = ACC_STAGES * BN;         // ring of STAGES scale slots follows
     static constexpr int TMEM_COLS = 512;
-    static constexpr int SMEM = STAGES * STAGE_BYTES + 256 + 1024;
-    static_assert(SF_COL0 + 2 * SF_COLS <= TMEM_COLS, "tensor memory budget");
+    static constexpr int STG_BYTES = 4 * 4096;              // epilogue staging, 4 KB per epilogue warp
+    static constexpr int SMEM = STAGES * STAGE_BYTES + STG_BYTES + 512 + 1024;
+    static_assert(SF_COL0 + STAGES * SF_COLS <= TMEM_COLS, "tensor memory budget");
+    static_assert(SMEM <= 232448, "shared memory budget");
 };
 
 struct GemmParams {
@@ -52,7 +61,6 @@ struct GemmParams {
     float alpha;
     const uint8_t* mask;     // [M, N/8] or NULL
     float had_scale;
-    void* d;
     int d_f32;
 };
 
@@ -74,10 +82,6 @@ __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::
 __device__ __forceinline__ void tc_commit(uint64_t* bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
                  : "memory");
-}
-// 32 rows x 16 bytes of shared memory -> 4 TMEM columns, replicated into all four lane quadrants
-__device__ __forceinline__ void tc_cp_sf(uint32_t taddr, uint64_t sdesc) {
-    asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(sdesc) : "memory");
 }
 __device__ __forceinline__ void tc_mma_mxf4(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
                                             uint32_t sfa_tmem, uint32_t sfb_tmem, uint32_t accumulate) {
@@ -101,24 +105,27 @@ __device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32]) {
         : "memory");
 }
 __device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+// registers -> 4 / 8 consecutive TMEM columns of this warp's 32 lanes (one value per lane and column)
+__device__ __forceinline__ void tc_st4(uint32_t taddr, const uint32_t (&r)[8]) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x4.b32 [%0], {%1, %2, %3, %4};" ::"r"(taddr), "r"(r[0]), "r"(r[1]),
+                 "r"(r[2]), "r"(r[3])
+                 : "memory");
+}
+__device__ __forceinline__ void tc_st8(uint32_t taddr, const uint32_t (&r)[8]) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"r"(taddr), "r"(r[0]),
+                 "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
+                 : "memory");
+}
+__device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
 // Shared-memory matrix descriptor, K-major operand, 128-byte swizzle: rows are 128 B apart,
 // groups of 8 rows 1024 B apart.
 __device__ __forceinline__ uint64_t make_desc_sw128(uint32_t saddr) {
     uint64_t d = 0;
     d |= (uint64_t)((saddr & 0x3FFFFu) >> 4);       // start address
-    d |= (uint64_t)0 << 16;                          // leading byte offset (unused for swizzled K-major)
-    d |= (uint64_t)(1024 >> 4) << 32;                // stride byte offset
+    d |= (uint64_t)(1024 >> 4) << 32;                // stride byte offset (leading offset unused here)
     d |= (uint64_t)1 << 46;                          // descriptor version (sm_100)
     d |= (uint64_t)2 << 61;                          // SWIZZLE_128B
-    return d;
-}
-// Descriptor for one 512-byte scale block: 32 rows x 16 B, no swizzle, 8-row groups 128 B apart.
-__device__ __forceinline__ uint64_t make_desc_sf(uint32_t saddr) {
-    uint64_t d = 0;
-    d |= (uint64_t)((saddr & 0x3FFFFu) >> 4);
-    d |= (uint64_t)(128 >> 4) << 32;
-    d |= (uint64_t)1 << 46;
     return d;
 }
 // Instruction descriptor, kind::mxf4, E2M1 x E2M1, UE8M0 scales, both operands K-major, M = 128.
@@ -155,18 +162,21 @@ __device__ __forceinline__ bool gemm_wait(uint64_t* bar, uint32_t parity, int32_
 template <int BN>
 __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_mxfp4_kernel(const __grid_constant__ CUtensorMap tm_a,
                                                                     const __grid_constant__ CUtensorMap tm_b,
+                                                                    const __grid_constant__ CUtensorMap tm_d,
                                                                     const GemmParams p) {
     using C = GemmCfg<BN>;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* s_a = smem;
     uint8_t* s_b = s_a + C::STAGES * C::A_BYTES;
-    uint8_t* s_sfa = s_b + C::STAGES * C::B_BYTES;
+    uint8_t* s_stg = s_b + C::STAGES * C::B_BYTES;           // 1024-aligned
+    uint8_t* s_sfa = s_stg + C::STG_BYTES;
     uint8_t* s_sfb = s_sfa + C::STAGES * C::SFA_BYTES;
     uint64_t* bars = reinterpret_cast<uint64_t*>(s_sfb + C::STAGES * C::SFB_BYTES);
     uint64_t* full = bars;
     uint64_t* empty = full + C::STAGES;
-    uint64_t* acc_full = empty + C::STAGES;
+    uint64_t* sf_full = empty + C::STAGES;
+    uint64_t* acc_full = sf_full + C::STAGES;
     uint64_t* acc_empty = acc_full + C::ACC_STAGES;
     uint32_t* s_tmem = reinterpret_cast<uint32_t*>(acc_empty + C::ACC_STAGES);
     volatile int* dead = reinterpret_cast<volatile int*>(s_tmem + 1);
@@ -177,6 +187,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_mxfp4_kernel(const __gri
         for (int i = 0; i < C::STAGES; ++i) {
             mbar_init(&full[i], 1);
             mbar_init(&empty[i], 1);
+            mbar_init(&sf_full[i], 4);
         }
         for (int i = 0; i < C::ACC_STAGES; ++i) {
             mbar_init(&acc_full[i], 1);
@@ -186,6 +197,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_mxfp4_kernel(const __gri
         fence_mbar_init();
         prefetch_tmap(&tm_a);
         prefetch_tmap(&tm_b);
+        prefetch_tmap(&tm_d);
     }
     if (warp == 1) {
         tmem_alloc(s_tmem, C::TMEM_COLS);
@@ -207,20 +219,21 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_mxfp4_kernel(const __gri
             for (int tile = blockIdx.x; tile < n_tiles_total && !*dead; tile += gridDim.x) {
                 const int m_blk = tile % p.m_tiles, n_blk = tile / p.m_tiles;
                 const int m0 = m_blk * BM, n0 = n_blk * BN;
-                const int n_rowblocks = min(BN / 128, (p.N - n0) / 128);
+                const int blk0 = n0 / 128;
+                const int n_blocks = (min(n0 + BN, p.N) - 1) / 128 - blk0 + 1;
                 for (int ks = 0; ks < k_stages; ++ks, ++it) {
                     const int s = it % C::STAGES;
                     const uint32_t ph = (it / C::STAGES) & 1;
                     if (!gemm_wait(&empty[s], ph ^ 1, WAIT_GEMM_EMPTY, dead)) break;
                     const int nch = min(2, p.k_chunks - 2 * ks);
-                    mbar_arrive_expect_tx(&full[s], C::A_BYTES + C::B_BYTES + nch * 512 * (1 + n_rowblocks));
+                    mbar_arrive_expect_tx(&full[s], C::A_BYTES + C::B_BYTES + nch * 512 * (1 + n_blocks));
                     tma_load_2d(s_a + s * C::A_BYTES, &tm_a, ks * BK_BYTES, m0, &full[s]);
                     tma_load_2d(s_b + s * C::B_BYTES, &tm_b, ks * BK_BYTES, n0, &full[s]);
                     bulk_load(s_sfa + s * C::SFA_BYTES, p.a_sf + ((int64_t)m_blk * sf_blocks_per_rowblock + 2 * ks) * 512,
                               nch * 512, &full[s]);
-                    for (int rb = 0; rb < n_rowblocks; ++rb)
+                    for (int rb = 0; rb < n_blocks; ++rb)
                         bulk_load(s_sfb + s * C::SFB_BYTES + rb * 1024,
-                                  p.b_sf + ((int64_t)(n0 / 128 + rb) * sf_blocks_per_rowblock + 2 * ks) * 512, nch * 512,
+                                  p.b_sf + ((int64_t)(blk0 + rb) * sf_blocks_per_rowblock + 2 * ks) * 512, nch * 512,
                                   &full[s]);
                 }
             }
@@ -230,8 +243,6 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_mxfp4_kernel(const __gri
         if (lane == 0) {
             uint32_t it = 0, acc_it = 0;
             for (int tile = blockIdx.x; tile < n_tiles_total && !*dead; tile += gridDim.x, ++acc_it) {
-                const int n0 = (tile / p.m_tiles) * BN;
-                const int n_rowblocks = min(BN / 128, (p.N - n0) / 128);
                 const int as = acc_it % C::ACC_STAGES;
                 const uint32_t aph = (acc_it / C::ACC_STAGES) & 1;
                 if (!gemm_wait(&acc_empty[as], aph ^ 1, WAIT_GEMM_ACC_EMPTY, dead)) break;
@@ -241,26 +252,19 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_mxfp4_kernel(const __gri
                     const int s = it % C::STAGES;
                     const uint32_t ph = (it / C::STAGES) & 1;
                     if (!gemm_wait(&full[s], ph, WAIT_GEMM_FULL, dead)) break;
+                    if (!gemm_wait(&sf_full[s], ph, WAIT_GEMM_SF, dead)) break;
                     tc_fence_after();
                     const int nch = min(2, p.k_chunks - 2 * ks);
-                    const uint32_t sf_tmem = tmem_base + C::SF_COL0 + (it & 1) * C::SF_COLS;
-                    const uint32_t sa = smem_u32(s_a + s * C::A_BYTES);
-                    const uint32_t sb = smem_u32(s_b + s * C::B_BYTES);
-                    const uint32_t ssfa = smem_u32(s_sfa + s * C::SFA_BYTES);
-                    const uint32_t ssfb = smem_u32(s_sfb + s * C::SFB_BYTES);
-                    for (int c = 0; c < nch; ++c) {
-                        tc_cp_sf(sf_tmem + c * 4, make_desc_sf(ssfa + c * 512));
-                        for (int rb = 0; rb < n_rowblocks; ++rb)
-                            tc_cp_sf(sf_tmem + 8 + c * (BN / 32) + rb * 4, make_desc_sf(ssfb + rb * 1024 + c * 512));
-                    }
-                    const uint64_t adesc = make_desc_sw128(sa), bdesc = make_desc_sw128(sb);
+                    const uint32_t sf_tmem = tmem_base + C::SF_COL0 + s * C::SF_COLS;
+                    const uint64_t adesc = make_desc_sw128(smem_u32(s_a + s * C::A_BYTES));
+                    const uint64_t bdesc = make_desc_sw128(smem_u32(s_b + s * C::B_BYTES));
                     for (int c = 0; c < nch; ++c) {
 #pragma unroll
                         for (int j = 0; j < 2; ++j) {
                             const uint32_t koff = (uint32_t)((c * 2 + j) * 32) >> 4;  // 64 elements = 32 bytes
                             const uint32_t sfid = (uint32_t)j * 2u;
                             tc_mma_mxf4(d_tmem, adesc + koff, bdesc + koff, make_idesc(BN, sfid),
-                                        (sf_tmem + c * 4) | (sfid << 30), (sf_tmem + 8 + c * (BN / 32)) | (sfid << 30),
+                                        (sf_tmem + c * 4) | (sfid << 30), (sf_tmem + 8 + c * C::SFB_ST) | (sfid << 30),
                                         (ks | c | j) != 0);
                         }
                     }
@@ -269,10 +273,50 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_mxfp4_kernel(const __gri
                 tc_commit(&acc_full[as]);  // accumulator complete
             }
         }
+    } else if (warp >= 6) {
+        // ------------------------------ scale feeders ------------------------------
+        // Each of the four warps copies the stage's scale bytes from shared memory into its own
+        // 32-lane quadrant of tensor memory: row r of a 128-row block lives in lane r % 32, 32-bit
+        // column r / 32 (one byte per 32-element K-block), replicated in all four quadrants.
+        const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
+        uint32_t it = 0;
+        for (int tile = blockIdx.x; tile < n_tiles_total && !*dead; tile += gridDim.x) {
+            const int n0 = (tile / p.m_tiles) * BN;
+            const int seg0 = (n0 % 128) / 32;  // first 32-row segment of the tile inside its first scale block
+            for (int ks = 0; ks < k_stages; ++ks, ++it) {
+                const int s = it % C::STAGES;
+                const uint32_t ph = (it / C::STAGES) & 1;
+                if (!gemm_wait(&full[s], ph, WAIT_GEMM_FULL, dead)) break;
+                const int nch = min(2, p.k_chunks - 2 * ks);
+                const uint32_t sf_tmem = tmem_base + lane_base + C::SF_COL0 + s * C::SF_COLS;
+                const uint8_t* sfa = s_sfa + s * C::SFA_BYTES + lane * 16;
+                const uint8_t* sfb = s_sfb + s * C::SFB_BYTES + lane * 16;
+                for (int c = 0; c < nch; ++c) {
+                    uint32_t r[8];
+                    const uint4 va = *reinterpret_cast<const uint4*>(sfa + c * 512);
+                    r[0] = va.x, r[1] = va.y, r[2] = va.z, r[3] = va.w;
+                    tc_st4(sf_tmem + c * 4, r);
+#pragma unroll
+                    for (int j = 0; j < C::SFB_ST; ++j) {
+                        const int seg = seg0 + j;
+                        r[j] = j < C::NSEG ? *reinterpret_cast<const uint32_t*>(sfb + (seg >> 2) * 1024 + c * 512 + (seg & 3) * 4) : 0u;
+                    }
+                    if (C::SFB_ST == 4)
+                        tc_st4(sf_tmem + 8 + c * C::SFB_ST, r);
+                    else
+                        tc_st8(sf_tmem + 8 + c * C::SFB_ST, r);
+                }
+                tc_wait_st();
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&sf_full[s]);
+            }
+        }
     } else {
         // ------------------------------ epilogue ------------------------------
         const int q = warp & 3;  // TMEM lane quadrant this warp may read
-        uint32_t acc_it = 0;
+        uint8_t* stg = s_stg + (warp - 2) * 4096;
+        uint32_t acc_it = 0, n_stores = 0;
         for (int tile = blockIdx.x; tile < n_tiles_total && !*dead; tile += gridDim.x, ++acc_it) {
             const int m_blk = tile % p.m_tiles, n_blk = tile / p.m_tiles;
             const int n0 = n_blk * BN;
@@ -280,16 +324,17 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_mxfp4_kernel(const __gri
             const uint32_t aph = (acc_it / C::ACC_STAGES) & 1;
             if (!gemm_wait(&acc_full[as], aph, WAIT_GEMM_ACC_FULL, dead)) break;
             tc_fence_after();
-            const int64_t row = (int64_t)m_blk * BM + q * 32 + lane;
+            const int row0 = m_blk * BM + q * 32;
+            const int64_t row = (int64_t)row0 + lane;
             const int n_chunks = min(BN, p.N - n0) / 32;
-            for (int ch = 0; ch < n_chunks; ++ch) {
+            for (int ch = 0; ch < n_chunks; ++ch, ++n_stores) {
                 uint32_t r[32];
                 tc_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + C::ACC_COL0 + as * BN + ch * 32, r);
                 tc_wait_ld();
                 float v[32];
 #pragma unroll
                 for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) * p.alpha;
-                const int64_t col = (int64_t)n0 + ch * 32;
+                const int col = n0 + ch * 32;
                 if (p.mask) {
                     const uint32_t m = *reinterpret_cast<const uint32_t*>(p.mask + row * (p.N >> 3) + (col >> 3));
 #pragma unroll
@@ -298,12 +343,26 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_mxfp4_kernel(const __gri
 #pragma unroll
                     for (int i = 0; i < 32; ++i) v[i] *= p.had_scale;
                 }
+                // stage the 32 x 32 block in (swizzled) shared memory and hand it to TMA
                 if (p.d_f32) {
-                    float4* o = reinterpret_cast<float4*>(static_cast<float*>(p.d) + row * p.N + col);
+                    if (lane == 0) bulk_wait_read0();
+                    __syncwarp();
+                    uint8_t* dst = stg + lane * 128;
 #pragma unroll
-                    for (int j = 0; j < 8; ++j) o[j] = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+                    for (int j = 0; j < 8; ++j)
+                        *reinterpret_cast<float4*>(dst + ((j ^ (lane & 7)) << 4)) =
+                            make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+                    fence_proxy_async_smem();
+                    __syncwarp();
+                    if (lane == 0) {
+                        tma_store_2d(&tm_d, col, row0, stg);
+                        bulk_commit();
+                    }
                 } else {
-                    uint4* o = reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.d) + row * p.N + col);
+                    uint8_t* buf = stg + (n_stores & 1) * 2048;
+                    if (lane == 0) bulk_wait_read1();
+                    __syncwarp();
+                    uint8_t* dst = buf + lane * 64;
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {
                         uint32_t w[4];
@@ -312,7 +371,13 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_mxfp4_kernel(const __gri
                             __nv_bfloat162 t = __floats2bfloat162_rn(v[8 * j + 2 * k], v[8 * j + 2 * k + 1]);
                             w[k] = *reinterpret_cast<uint32_t*>(&t);
                         }
-                        o[j] = make_uint4(w[0], w[1], w[2], w[3]);
+                        *reinterpret_cast<uint4*>(dst + ((j ^ ((lane >> 1) & 3)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+                    }
+                    fence_proxy_async_smem();
+                    __syncwarp();
+                    if (lane == 0) {
+                        tma_store_2d(&tm_d, col, row0, buf);
+                        bulk_commit();
                     }
                 }
             }
@@ -320,6 +385,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_mxfp4_kernel(const __gri
             __syncwarp();
             if (lane == 0) mbar_arrive(&acc_empty[as]);
         }
+        if (lane == 0) bulk_wait0();
     }
 
     // ------------------------------ wind-down ------------------------------
@@ -337,14 +403,19 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_mxfp4_kernel(const __gri
 }
 
 template <int BN>
-static int launch_gemm(const uint8_t* a, const uint8_t* b, const GemmParams& p0, cudaStream_t stream) {
+static int launch_gemm(const uint8_t* a, const uint8_t* b, void* d, const GemmParams& p0, cudaStream_t stream) {
     using C = GemmCfg<BN>;
     GemmParams p = p0;
     p.n_tiles = (p.N + BN - 1) / BN;
-    CUtensorMap tm_a, tm_b;
+    CUtensorMap tm_a, tm_b, tm_d;
     int rc = make_tmap_2d(&tm_a, a, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, p.K / 2, p.M, p.K / 2, BK_BYTES, BM, 3);
     if (rc) return rc;
     rc = make_tmap_2d(&tm_b, b, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, p.K / 2, p.N, p.K / 2, BK_BYTES, p.N < BN ? p.N : BN, 3);
+    if (rc) return rc;
+    if (p.d_f32)
+        rc = make_tmap_2d(&tm_d, d, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, p.N, p.M, (uint64_t)p.N * 4, 32, 32, 3);
+    else
+        rc = make_tmap_2d(&tm_d, d, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, p.N, p.M, (uint64_t)p.N * 2, 32, 32, 2);
     if (rc) return rc;
     auto kern = gemm_mxfp4_kernel<BN>;
     rc = check_cuda(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM), "cudaFuncSetAttribute");
@@ -354,7 +425,7 @@ static int launch_gemm(const uint8_t* a, const uint8_t* b, const GemmParams& p0,
     if ((rc = check_cuda(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev), "cudaDeviceGetAttribute"))) return rc;
     const int tiles = p.m_tiles * p.n_tiles;
     const int grid = tiles < sms ? tiles : sms;
-    kern<<<grid, GEMM_THREADS, C::SMEM, stream>>>(tm_a, tm_b, p);
+    kern<<<grid, GEMM_THREADS, C::SMEM, stream>>>(tm_a, tm_b, tm_d, p);
     return check_cuda(cudaGetLastError(), "gemm launch");
 }
 
@@ -385,7 +456,7 @@ extern "C" __attribute__((visibility("default"))) int quartet_gemm_mxfp4_tn(cons
     p.k_chunks = (int)(K / 128);
     p.m_tiles = (int)(M / BM);
     p.alpha = alpha, p.mask = mask, p.had_scale = had_scale;
-    p.d = d, p.d_f32 = d_dtype == QUARTET_F32;
+    p.d_f32 = d_dtype == QUARTET_F32;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     // Tile width: 256 unless the output is narrow or not a multiple of 256.  QUARTET_GEMM_BN=128|256
     // overrides the choice (tuning aid).
@@ -394,6 +465,6 @@ extern "C" __attribute__((visibility("default"))) int quartet_gemm_mxfp4_tn(cons
         return e ? atoi(e) : 0;
     }();
     const bool wide = forced_bn ? forced_bn == 256 : (N % 256 == 0 || N > 1024);
-    if (wide) return launch_gemm<256>(a, b, p, s);
-    return launch_gemm<128>(a, b, p, s);
+    if (wide) return launch_gemm<256>(a, b, d, p, s);
+    return launch_gemm<128>(a, b, d, p, s);
 }
