@@ -19,12 +19,18 @@
 //               block in swizzled shared memory, TMA store
 // Every wait is bounded; a wait that gives up records itself in the fault word and the CTA
 // winds down (frees its TMEM) instead of hanging.
+#include <cstdio>
 #include <cstdlib>
 
 #include "common.cuh"
 #include "quant_math.cuh"
 
 namespace quartet {
+
+// event trace for tuning (QUARTET_GEMM_DEBUG bit 256): [event kind][stage iteration] -> SM clock, CTA 0 only
+__device__ long long g_trace[16][64];
+#define TRACE(kind, idx) do { if ((p.dbg & 256) && blockIdx.x == 0 && (idx) < 64) g_trace[kind][idx] = clock64(); } while (0)
+#define TRACE1(kind, idx) do { if ((p.dbg & 256) && blockIdx.x == 1 && (idx) < 64) g_trace[kind][idx] = clock64(); } while (0)
 
 constexpr int BM = 128;
 constexpr int BK_BYTES = 128;   // 256 e2m1 elements per stage along K
@@ -62,6 +68,7 @@ struct GemmParams {
     const uint8_t* mask;     // [M, N/8] or NULL
     float had_scale;
     int d_f32;
+    int dbg;
 };
 
 // ---------------------------------------------------------------------------
@@ -225,6 +232,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_mxfp4_kernel(const __gri
                     const int s = it % C::STAGES;
                     const uint32_t ph = (it / C::STAGES) & 1;
                     if (!gemm_wait(&empty[s], ph ^ 1, WAIT_GEMM_EMPTY, dead)) break;
+                    TRACE(0, it);
                     const int nch = min(2, p.k_chunks - 2 * ks);
                     mbar_arrive_expect_tx(&full[s], C::A_BYTES + C::B_BYTES + nch * 512 * (1 + n_blocks));
                     tma_load_2d(s_a + s * C::A_BYTES, &tm_a, ks * BK_BYTES, m0, &full[s]);
@@ -252,13 +260,15 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_mxfp4_kernel(const __gri
                     const int s = it % C::STAGES;
                     const uint32_t ph = (it / C::STAGES) & 1;
                     if (!gemm_wait(&full[s], ph, WAIT_GEMM_FULL, dead)) break;
+                    TRACE(1, it);
                     if (!gemm_wait(&sf_full[s], ph, WAIT_GEMM_SF, dead)) break;
+                    TRACE(2, it);
                     tc_fence_after();
                     const int nch = min(2, p.k_chunks - 2 * ks);
                     const uint32_t sf_tmem = tmem_base + C::SF_COL0 + s * C::SF_COLS;
                     const uint64_t adesc = make_desc_sw128(smem_u32(s_a + s * C::A_BYTES));
                     const uint64_t bdesc = make_desc_sw128(smem_u32(s_b + s * C::B_BYTES));
-                    for (int c = 0; c < nch; ++c) {
+                    for (int c = 0; c < nch && !(p.dbg & 2); ++c) {
 #pragma unroll
                         for (int j = 0; j < 2; ++j) {
                             const uint32_t koff = (uint32_t)((c * 2 + j) * 32) >> 4;  // 64 elements = 32 bytes
@@ -269,6 +279,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_mxfp4_kernel(const __gri
                         }
                     }
                     tc_commit(&empty[s]);  // frees the stage once the MMAs above have read it
+                    TRACE(3, it);
                 }
                 tc_commit(&acc_full[as]);  // accumulator complete
             }
@@ -287,11 +298,12 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_mxfp4_kernel(const __gri
                 const int s = it % C::STAGES;
                 const uint32_t ph = (it / C::STAGES) & 1;
                 if (!gemm_wait(&full[s], ph, WAIT_GEMM_FULL, dead)) break;
+                if (warp == 6 && lane == 0) TRACE(4, it);
                 const int nch = min(2, p.k_chunks - 2 * ks);
                 const uint32_t sf_tmem = tmem_base + lane_base + C::SF_COL0 + s * C::SF_COLS;
                 const uint8_t* sfa = s_sfa + s * C::SFA_BYTES + lane * 16;
                 const uint8_t* sfb = s_sfb + s * C::SFB_BYTES + lane * 16;
-                for (int c = 0; c < nch; ++c) {
+                for (int c = 0; c < nch && !(p.dbg & 4); ++c) {
                     uint32_t r[8];
                     const uint4 va = *reinterpret_cast<const uint4*>(sfa + c * 512);
                     r[0] = va.x, r[1] = va.y, r[2] = va.z, r[3] = va.w;
@@ -310,6 +322,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_mxfp4_kernel(const __gri
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&sf_full[s]);
+                if (warp == 6 && lane == 0) TRACE(5, it);
             }
         }
     } else {
@@ -327,7 +340,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_mxfp4_kernel(const __gri
             const int row0 = m_blk * BM + q * 32;
             const int64_t row = (int64_t)row0 + lane;
             const int n_chunks = min(BN, p.N - n0) / 32;
-            for (int ch = 0; ch < n_chunks; ++ch, ++n_stores) {
+            for (int ch = 0; ch < n_chunks && !(p.dbg & 8); ++ch, ++n_stores) {
                 uint32_t r[32];
                 tc_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + C::ACC_COL0 + as * BN + ch * 32, r);
                 tc_wait_ld();
@@ -402,6 +415,437 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_mxfp4_kernel(const __gri
     }
 }
 
+// ===========================================================================================
+// Two-CTA variant (cta_group::2): a cluster of two CTAs on one TPC computes a 256 x BN tile.
+// Each CTA stages its own 128 rows of A and HALF of the B tile (BN/2 rows); one thread of the
+// leader CTA issues MMAs that read both CTAs' shared memory and accumulate into both CTAs' tensor
+// memory (rows 0-127 of the tile in the leader, 128-255 in its peer).  Per output element this
+// halves the B traffic through shared memory and cuts the L2 -> SM operand traffic by a third,
+// which is what bounds the one-CTA kernel.  Scales: each CTA feeds SFA of its own rows and SFB of
+// the whole tile into its own tensor memory.  Cross-CTA signalling uses remote mbarrier arrives
+// and tcgen05.commit onto the peer's barriers; no multicast copy is involved.
+// ===========================================================================================
+template <int BN>
+struct Gemm2Cfg {
+    static constexpr int STAGES = 5;
+    static constexpr int A_BYTES = BM * BK_BYTES;            // 16 KB
+    static constexpr int B_BYTES = (BN / 2) * BK_BYTES;      // this CTA's half of the B tile
+    static constexpr int SFA_BYTES = 1024;
+    static constexpr int SFB_BLOCKS = BN / 128;
+    static constexpr int SFB_BYTES = SFB_BLOCKS * 1024;
+    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES + SFA_BYTES + SFB_BYTES;
+    static constexpr int NSEG = BN / 32;
+    static constexpr int SFB_ST = NSEG <= 4 ? 4 : 8;
+    static constexpr int SF_COLS = 8 + 2 * SFB_ST;
+    static constexpr int SF_COL0 = BN;
+    static constexpr int TMEM_COLS = 512;
+    static constexpr int STG_BYTES = 4 * 4096;
+    static constexpr int SMEM = STAGES * STAGE_BYTES + STG_BYTES + 512 + 1024;
+    static_assert(SF_COL0 + STAGES * SF_COLS <= TMEM_COLS, "tensor memory budget");
+    static_assert(SMEM <= 232448, "shared memory budget");
+};
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ uint32_t mapa_u32(uint32_t saddr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(saddr), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+    // default semantics (as the pipelines of CUTLASS use for consumer -> producer signalling across
+    // CTAs); an explicit .release.cluster here costs ~1500 cycles per arrive
+    asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait_cluster(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.b32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.b32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ bool gemm_wait_cluster(uint64_t* bar, uint32_t parity, int32_t who, volatile int* dead, bool plain = false) {
+    if (*dead) return false;
+    uint64_t t0 = 0;
+    for (uint32_t i = 0;; ++i) {
+        if (plain ? mbar_test_wait(bar, parity) : mbar_try_wait_cluster(bar, parity)) return true;
+        if ((i & 1023u) == 1023u) {
+            uint64_t now;
+            asm volatile("mov.u64 %0, %globaltimer;" : "=l"(now));
+            if (t0 == 0) t0 = now;
+            if (now - t0 > 2000000000ull || *dead) break;
+        }
+    }
+    atomicOr(&g_status, who | 0x200);
+    *dead = 1;
+    return false;
+}
+__device__ __forceinline__ void tmem_alloc2(uint32_t* dst_smem, uint32_t ncols) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(dst_smem)), "r"(ncols)
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish2() {
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc2(uint32_t taddr, uint32_t ncols) {
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+// arrive on a barrier (given by its shared::cluster address) once all MMAs issued so far are done
+__device__ __forceinline__ void tc_commit2(uint32_t cluster_addr) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(cluster_addr)
+                 : "memory");
+}
+__device__ __forceinline__ void tc_mma2_mxf4(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                             uint32_t sfa_tmem, uint32_t sfb_tmem, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::mxf4.block_scale.block32 [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
+        :
+        : "r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(sfa_tmem), "r"(sfb_tmem)
+        : "memory");
+}
+__device__ __forceinline__ uint32_t make_idesc2(int n, uint32_t sf_id) {
+    uint32_t d = 0;
+    d |= sf_id << 4;
+    d |= 1u << 7;
+    d |= 1u << 10;
+    d |= (uint32_t)(n >> 3) << 17;
+    d |= 1u << 23;
+    d |= (uint32_t)(256 >> 4) << 24;    // M = 256 across the CTA pair
+    d |= sf_id << 29;
+    return d;
+}
+
+template <int BN>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
+    gemm_mxfp4_2cta_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
+                           const __grid_constant__ CUtensorMap tm_d, const GemmParams p) {
+    using C = Gemm2Cfg<BN>;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t* s_a = smem;
+    uint8_t* s_b = s_a + C::STAGES * C::A_BYTES;
+    uint8_t* s_stg = s_b + C::STAGES * C::B_BYTES;
+    uint8_t* s_sfa = s_stg + C::STG_BYTES;
+    uint8_t* s_sfb = s_sfa + C::STAGES * C::SFA_BYTES;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(s_sfb + C::STAGES * C::SFB_BYTES);
+    uint64_t* full = bars;                      // local: this CTA's copies of a stage have landed
+    uint64_t* empty = full + C::STAGES;         // local: the pair's MMAs are done with the stage
+    uint64_t* sf_full = empty + C::STAGES;      // leader only: 8 feeder warps (both CTAs) have fed the stage
+    uint64_t* acc_full = sf_full + C::STAGES;   // local: accumulator complete
+    uint64_t* acc_empty = acc_full + 1;         // leader only: 8 epilogue warps (both CTAs) have drained it
+    uint32_t* s_tmem = reinterpret_cast<uint32_t*>(acc_empty + 1);
+    volatile int* dead = reinterpret_cast<volatile int*>(s_tmem + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_ctarank();
+    const bool leader = rank == 0;
+
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < C::STAGES; ++i) {
+            mbar_init(&full[i], 1);
+            mbar_init(&empty[i], 1);
+            mbar_init(&sf_full[i], 8);
+        }
+        mbar_init(acc_full, 1);
+        mbar_init(acc_empty, 8);
+        *dead = 0;
+        fence_mbar_init();
+        prefetch_tmap(&tm_a);
+        prefetch_tmap(&tm_b);
+        prefetch_tmap(&tm_d);
+    }
+    __syncthreads();
+    if (warp == 1) {
+        tmem_alloc2(s_tmem, C::TMEM_COLS);
+        tmem_relinquish2();
+    }
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();  // both CTAs' barriers are initialised before any remote arrive / commit
+    tc_fence_after();
+    const uint32_t tmem_base = *s_tmem;
+
+    const int m_pairs = p.m_tiles >> 1;
+    const int n_tiles_total = m_pairs * p.n_tiles;
+    const int n_clusters = gridDim.x >> 1, cluster_id = blockIdx.x >> 1;
+    const int k_stages = (p.k_chunks + 1) >> 1;
+    const int64_t sf_blocks_per_rowblock = p.k_chunks;
+
+    if (warp == 0) {
+        // ------------------------------ TMA producer (both CTAs) ------------------------------
+        if (lane == 0) {
+            uint32_t it = 0;
+            for (int tile = cluster_id; tile < n_tiles_total && !*dead; tile += n_clusters) {
+                const int m_blk = (tile % m_pairs) * 2 + (int)rank, n_blk = tile / m_pairs;
+                const int m0 = m_blk * BM, n0 = n_blk * BN;
+                const int blk0 = n0 / 128;
+                const int n_blocks = (min(n0 + BN, p.N) - 1) / 128 - blk0 + 1;
+                for (int ks = 0; ks < k_stages; ++ks, ++it) {
+                    const int s = it % C::STAGES;
+                    const uint32_t ph = (it / C::STAGES) & 1;
+                    if (!gemm_wait(&empty[s], ph ^ 1, WAIT_GEMM_EMPTY, dead)) break;
+                    TRACE(0, it);
+                    TRACE1(6, it);
+                    const int nch = min(2, p.k_chunks - 2 * ks);
+                    mbar_arrive_expect_tx(&full[s], C::A_BYTES + C::B_BYTES + nch * 512 * (1 + n_blocks));
+                    tma_load_2d(s_a + s * C::A_BYTES, &tm_a, ks * BK_BYTES, m0, &full[s]);
+                    tma_load_2d(s_b + s * C::B_BYTES, &tm_b, ks * BK_BYTES, n0 + (int)rank * (BN / 2), &full[s]);
+                    bulk_load(s_sfa + s * C::SFA_BYTES, p.a_sf + ((int64_t)m_blk * sf_blocks_per_rowblock + 2 * ks) * 512,
+                              nch * 512, &full[s]);
+                    for (int rb = 0; rb < n_blocks; ++rb)
+                        bulk_load(s_sfb + s * C::SFB_BYTES + rb * 1024,
+                                  p.b_sf + ((int64_t)(blk0 + rb) * sf_blocks_per_rowblock + 2 * ks) * 512, nch * 512,
+                                  &full[s]);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------ MMA issuer (leader CTA only) ------------------------------
+        if (leader && lane == 0) {
+            uint32_t it = 0, acc_it = 0;
+            uint32_t empty_peer[C::STAGES];
+#pragma unroll
+            for (int i = 0; i < C::STAGES; ++i) empty_peer[i] = mapa_u32(smem_u32(&empty[i]), 1);
+            const uint32_t acc_full_peer = mapa_u32(smem_u32(acc_full), 1);
+            for (int tile = cluster_id; tile < n_tiles_total && !*dead; tile += n_clusters, ++acc_it) {
+                if (!gemm_wait_cluster(acc_empty, (acc_it & 1) ^ 1, WAIT_GEMM_ACC_EMPTY, dead)) break;
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base;
+                for (int ks = 0; ks < k_stages; ++ks, ++it) {
+                    const int s = it % C::STAGES;
+                    const uint32_t ph = (it / C::STAGES) & 1;
+                    if (!gemm_wait(&full[s], ph, WAIT_GEMM_FULL, dead)) break;
+                    TRACE(1, it);
+                    if (!gemm_wait_cluster(&sf_full[s], ph, WAIT_GEMM_SF, dead)) break;
+                    TRACE(2, it);
+                    tc_fence_after();
+                    const int nch = min(2, p.k_chunks - 2 * ks);
+                    const uint32_t sf_tmem = tmem_base + C::SF_COL0 + s * C::SF_COLS;
+                    const uint64_t adesc = make_desc_sw128(smem_u32(s_a + s * C::A_BYTES));
+                    const uint64_t bdesc = make_desc_sw128(smem_u32(s_b + s * C::B_BYTES));
+                    for (int c = 0; c < nch && !(p.dbg & 2); ++c) {
+#pragma unroll
+                        for (int j = 0; j < 2; ++j) {
+                            const uint32_t koff = (uint32_t)((c * 2 + j) * 32) >> 4;
+                            const uint32_t sfid = (uint32_t)j * 2u;
+                            tc_mma2_mxf4(d_tmem, adesc + koff, bdesc + koff, make_idesc2(BN, sfid),
+                                         (sf_tmem + c * 4) | (sfid << 30), (sf_tmem + 8 + c * C::SFB_ST) | (sfid << 30),
+                                         (ks | c | j) != 0);
+                            TRACE(8 + c * 2 + j, it);
+                        }
+                    }
+                    if ((p.dbg & 2) && (p.dbg & 128)) {  // no MMAs were issued: plain arrives are equivalent
+                        mbar_arrive(&empty[s]);
+                        mbar_arrive_cluster(empty_peer[s]);
+                    } else {
+                        tc_commit2(smem_u32(&empty[s]));
+                        TRACE(12, it);
+                        tc_commit2(empty_peer[s]);
+                    }
+                    TRACE(3, it);
+                }
+                tc_commit2(smem_u32(acc_full));
+                tc_commit2(acc_full_peer);
+            }
+        }
+    } else if (warp >= 6) {
+        // ------------------------------ scale feeders (both CTAs) ------------------------------
+        const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
+        uint32_t it = 0;
+        uint32_t sf_full_leader[C::STAGES];
+#pragma unroll
+        for (int i = 0; i < C::STAGES; ++i) sf_full_leader[i] = mapa_u32(smem_u32(&sf_full[i]), 0);
+        for (int tile = cluster_id; tile < n_tiles_total && !*dead; tile += n_clusters) {
+            const int n0 = (tile / m_pairs) * BN;
+            const int seg0 = (n0 % 128) / 32;
+            for (int ks = 0; ks < k_stages; ++ks, ++it) {
+                const int s = it % C::STAGES;
+                const uint32_t ph = (it / C::STAGES) & 1;
+                if (!gemm_wait(&full[s], ph, WAIT_GEMM_FULL, dead)) break;
+                if (warp == 6 && lane == 0) { TRACE(4, it); TRACE1(7, it); }
+                const int nch = min(2, p.k_chunks - 2 * ks);
+                const uint32_t sf_tmem = tmem_base + lane_base + C::SF_COL0 + s * C::SF_COLS;
+                const uint8_t* sfa = s_sfa + s * C::SFA_BYTES + lane * 16;
+                const uint8_t* sfb = s_sfb + s * C::SFB_BYTES + lane * 16;
+                for (int c = 0; c < nch && !(p.dbg & 4); ++c) {
+                    uint32_t r[8];
+                    const uint4 va = *reinterpret_cast<const uint4*>(sfa + c * 512);
+                    r[0] = va.x, r[1] = va.y, r[2] = va.z, r[3] = va.w;
+                    tc_st4(sf_tmem + c * 4, r);
+#pragma unroll
+                    for (int j = 0; j < C::SFB_ST; ++j) {
+                        const int seg = seg0 + j;
+                        r[j] = j < C::NSEG ? *reinterpret_cast<const uint32_t*>(sfb + (seg >> 2) * 1024 + c * 512 + (seg & 3) * 4) : 0u;
+                    }
+                    if (C::SFB_ST == 4)
+                        tc_st4(sf_tmem + 8 + c * C::SFB_ST, r);
+                    else
+                        tc_st8(sf_tmem + 8 + c * C::SFB_ST, r);
+                }
+                if (warp == 6 && lane == 0) TRACE(13, it);
+                tc_wait_st();
+                if (warp == 6 && lane == 0) TRACE(14, it);
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive_cluster(sf_full_leader[s]);
+                if (warp == 6 && lane == 0) TRACE(5, it);
+            }
+        }
+    } else {
+        // ------------------------------ epilogue (both CTAs) ------------------------------
+        const int q = warp & 3;
+        uint8_t* stg = s_stg + (warp - 2) * 4096;
+        const uint32_t acc_empty_leader = mapa_u32(smem_u32(acc_empty), 0);
+        uint32_t acc_it = 0, n_stores = 0;
+        for (int tile = cluster_id; tile < n_tiles_total && !*dead; tile += n_clusters, ++acc_it) {
+            const int m_blk = (tile % m_pairs) * 2 + (int)rank, n_blk = tile / m_pairs;
+            const int n0 = n_blk * BN;
+            if (!gemm_wait(acc_full, acc_it & 1, WAIT_GEMM_ACC_FULL, dead)) break;
+            tc_fence_after();
+            const int row0 = m_blk * BM + q * 32;
+            const int64_t row = (int64_t)row0 + lane;
+            const int n_chunks = min(BN, p.N - n0) / 32;
+            for (int ch = 0; ch < n_chunks && !(p.dbg & 8); ++ch, ++n_stores) {
+                uint32_t r[32];
+                tc_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + ch * 32, r);
+                tc_wait_ld();
+                float v[32];
+#pragma unroll
+                for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) * p.alpha;
+                const int col = n0 + ch * 32;
+                if (p.mask) {
+                    const uint32_t m = *reinterpret_cast<const uint32_t*>(p.mask + row * (p.N >> 3) + (col >> 3));
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) v[i] = ((m >> i) & 1u) ? v[i] : 0.f;
+                    wht32(v);
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) v[i] *= p.had_scale;
+                }
+                if (p.d_f32) {
+                    if (lane == 0) bulk_wait_read0();
+                    __syncwarp();
+                    uint8_t* dst = stg + lane * 128;
+#pragma unroll
+                    for (int j = 0; j < 8; ++j)
+                        *reinterpret_cast<float4*>(dst + ((j ^ (lane & 7)) << 4)) =
+                            make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+                    fence_proxy_async_smem();
+                    __syncwarp();
+                    if (lane == 0) {
+                        tma_store_2d(&tm_d, col, row0, stg);
+                        bulk_commit();
+                    }
+                } else {
+                    uint8_t* buf = stg + (n_stores & 1) * 2048;
+                    if (lane == 0) bulk_wait_read1();
+                    __syncwarp();
+                    uint8_t* dst = buf + lane * 64;
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        uint32_t w[4];
+#pragma unroll
+                        for (int k = 0; k < 4; ++k) {
+                            __nv_bfloat162 t = __floats2bfloat162_rn(v[8 * j + 2 * k], v[8 * j + 2 * k + 1]);
+                            w[k] = *reinterpret_cast<uint32_t*>(&t);
+                        }
+                        *reinterpret_cast<uint4*>(dst + ((j ^ ((lane >> 1) & 3)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+                    }
+                    fence_proxy_async_smem();
+                    __syncwarp();
+                    if (lane == 0) {
+                        tma_store_2d(&tm_d, col, row0, buf);
+                        bulk_commit();
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(acc_empty_leader);
+        }
+        if (lane == 0) bulk_wait0();
+    }
+
+    // ------------------------------ wind-down ------------------------------
+    __syncwarp();
+    tc_fence_before();
+    __syncthreads();
+    if (*dead) {
+        for (int i = 0; i < 2000; ++i) __nanosleep(1000);
+    }
+    cluster_sync_all();  // neither CTA leaves while its peer may still touch its barriers or memory
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc2(tmem_base, C::TMEM_COLS);
+    }
+}
+
+template <int BN>
+static int launch_gemm_2cta(const uint8_t* a, const uint8_t* b, void* d, const GemmParams& p0, cudaStream_t stream) {
+    using C = Gemm2Cfg<BN>;
+    GemmParams p = p0;
+    p.n_tiles = (p.N + BN - 1) / BN;
+    CUtensorMap tm_a, tm_b, tm_d;
+    int rc = make_tmap_2d(&tm_a, a, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, p.K / 2, p.M, p.K / 2, BK_BYTES, BM, 3);
+    if (rc) return rc;
+    rc = make_tmap_2d(&tm_b, b, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, p.K / 2, p.N, p.K / 2, BK_BYTES, BN / 2, 3);
+    if (rc) return rc;
+    if (p.d_f32)
+        rc = make_tmap_2d(&tm_d, d, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, p.N, p.M, (uint64_t)p.N * 4, 32, 32, 3);
+    else
+        rc = make_tmap_2d(&tm_d, d, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, p.N, p.M, (uint64_t)p.N * 2, 32, 32, 2);
+    if (rc) return rc;
+    auto kern = gemm_mxfp4_2cta_kernel<BN>;
+    rc = check_cuda(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM), "cudaFuncSetAttribute");
+    if (rc) return rc;
+    int dev = 0, sms = 0;
+    if ((rc = check_cuda(cudaGetDevice(&dev), "cudaGetDevice"))) return rc;
+    if ((rc = check_cuda(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev), "cudaDeviceGetAttribute"))) return rc;
+    // A persistent kernel must not launch more clusters than can be resident at once: on parts
+    // where some TPCs have a single SM enabled that is fewer than SMs / 2.
+    static thread_local int cached_dev = -1, cached_clusters = 0;
+    if (cached_dev != dev) {
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3((unsigned)sms, 1, 1);
+        cfg.blockDim = dim3(GEMM_THREADS, 1, 1);
+        cfg.dynamicSmemBytes = C::SMEM;
+        cudaLaunchAttribute attr;
+        attr.id = cudaLaunchAttributeClusterDimension;
+        attr.val.clusterDim.x = 2, attr.val.clusterDim.y = 1, attr.val.clusterDim.z = 1;
+        cfg.attrs = &attr, cfg.numAttrs = 1;
+        int n = 0;
+        if ((rc = check_cuda(cudaOccupancyMaxActiveClusters(&n, kern, &cfg), "cudaOccupancyMaxActiveClusters"))) return rc;
+        if (n < 1) return fail(QUARTET_E_CUDA, "no CTA pair can be resident");
+        cached_dev = dev, cached_clusters = n;
+        if (getenv("QUARTET_GEMM_VERBOSE")) fprintf(stderr, "quartet: %d SMs, %d resident CTA pairs\n", sms, n);
+    }
+    const int pair_tiles = (p.m_tiles / 2) * p.n_tiles;
+    const int clusters = pair_tiles < cached_clusters ? pair_tiles : cached_clusters;
+    kern<<<clusters * 2, GEMM_THREADS, C::SMEM, stream>>>(tm_a, tm_b, tm_d, p);
+    return check_cuda(cudaGetLastError(), "gemm (2-CTA) launch");
+}
+
 template <int BN>
 static int launch_gemm(const uint8_t* a, const uint8_t* b, void* d, const GemmParams& p0, cudaStream_t stream) {
     using C = GemmCfg<BN>;
@@ -431,6 +875,20 @@ static int launch_gemm(const uint8_t* a, const uint8_t* b, void* d, const GemmPa
 
 QUARTET_DEFINE_STATUS_READER(status_gemm)
 
+void dump_gemm_trace() {
+    static long long h[16][64];
+    cudaDeviceSynchronize();
+    if (cudaMemcpyFromSymbol(h, g_trace, sizeof(h)) != cudaSuccess) return;
+    const char* names[8] = {"prod:empty_ok", "mma:full_ok", "mma:sf_ok", "mma:commit", "feed:full_ok", "feed:arrive", "PEER prod:empty_ok", "PEER feed:full_ok"};
+    long long t0 = h[0][0], t1 = h[6][0];
+    for (int i = 0; i < 40; ++i) {
+        fprintf(stderr, "it %2d", i);
+        for (int k = 0; k < 8; ++k) fprintf(stderr, "  %s=%6lld", names[k], h[k][i] - (k < 6 ? t0 : t1));
+        fprintf(stderr, "\n      mma issue +%lld +%lld +%lld +%lld commit1 +%lld commit2 +%lld | feeder st-issued +%lld wait_st +%lld arrive +%lld", h[8][i] - h[2][i], h[9][i] - h[2][i], h[10][i] - h[2][i], h[11][i] - h[2][i], h[12][i] - h[2][i], h[3][i] - h[2][i], h[13][i] - h[4][i], h[14][i] - h[4][i], h[5][i] - h[4][i]);
+        fprintf(stderr, "\n");
+    }
+}
+
 }  // namespace quartet
 
 using namespace quartet;
@@ -457,6 +915,8 @@ extern "C" __attribute__((visibility("default"))) int quartet_gemm_mxfp4_tn(cons
     p.m_tiles = (int)(M / BM);
     p.alpha = alpha, p.mask = mask, p.had_scale = had_scale;
     p.d_f32 = d_dtype == QUARTET_F32;
+    static const int dbg = [] { const char* e = getenv("QUARTET_GEMM_DEBUG"); return e ? atoi(e) : 0; }();
+    p.dbg = dbg;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     // Tile width: 256 unless the output is narrow or not a multiple of 256.  QUARTET_GEMM_BN=128|256
     // overrides the choice (tuning aid).
@@ -464,7 +924,22 @@ extern "C" __attribute__((visibility("default"))) int quartet_gemm_mxfp4_tn(cons
         const char* e = getenv("QUARTET_GEMM_BN");
         return e ? atoi(e) : 0;
     }();
+    static const int forced_cta = [] {
+        const char* e = getenv("QUARTET_GEMM_CTAS");
+        return e ? atoi(e) : 0;
+    }();
     const bool wide = forced_bn ? forced_bn == 256 : (N % 256 == 0 || N > 1024);
-    if (wide) return launch_gemm<256>(a, b, d, p, s);
+    // CTA pairs need an even number of 128-row tiles; QUARTET_GEMM_CTAS=1|2 overrides (tuning aid).
+    const bool pair = forced_cta ? forced_cta == 2 : true;
+    if (pair && wide && M % 256 == 0) {
+        int r = launch_gemm_2cta<256>(a, b, d, p, s);
+        if (p.dbg & 256) dump_gemm_trace();
+        return r;
+    }
+    if (wide) {
+        int r = launch_gemm<256>(a, b, d, p, s);
+        if (p.dbg & 256) dump_gemm_trace();
+        return r;
+    }
     return launch_gemm<128>(a, b, d, p, s);
 }
