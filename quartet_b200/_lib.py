@@ -9,7 +9,8 @@ import ctypes as C
 import os
 
 _PKG = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_PKG, "lib", "libquartet_b200.so")
+# QUARTET_B200_LIB points at an alternative build of the same library (e.g. one compiled with tracing)
+LIB_PATH = os.environ.get("QUARTET_B200_LIB") or os.path.join(_PKG, "lib", "libquartet_b200.so")
 
 _p, _i, _i64, _u32, _u64, _f = C.c_void_p, C.c_int, C.c_int64, C.c_uint32, C.c_uint64, C.c_float
 

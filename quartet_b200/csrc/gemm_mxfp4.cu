@@ -27,10 +27,16 @@
 
 namespace quartet {
 
-// event trace for tuning (QUARTET_GEMM_DEBUG bit 256): [event kind][stage iteration] -> SM clock, CTA 0 only
+// Pipeline event trace, compiled in only with -DQUARTET_GEMM_TRACE (a tuning aid): CTA 0 (and its
+// peer, CTA 1) record the SM clock of up to 64 stage iterations per event kind.
+#ifdef QUARTET_GEMM_TRACE
 __device__ long long g_trace[16][64];
-#define TRACE(kind, idx) do { if ((p.dbg & 256) && blockIdx.x == 0 && (idx) < 64) g_trace[kind][idx] = clock64(); } while (0)
-#define TRACE1(kind, idx) do { if ((p.dbg & 256) && blockIdx.x == 1 && (idx) < 64) g_trace[kind][idx] = clock64(); } while (0)
+#define TRACE(kind, idx) do { if (blockIdx.x == 0 && (idx) < 64) g_trace[kind][idx] = clock64(); } while (0)
+#define TRACE_PEER(kind, idx) do { if (blockIdx.x == 1 && (idx) < 64) g_trace[kind][idx] = clock64(); } while (0)
+#else
+#define TRACE(kind, idx)
+#define TRACE_PEER(kind, idx)
+#endif
 
 constexpr int BM = 128;
 constexpr int BK_BYTES = 128;   // 256 e2m1 elements per stage along K
@@ -68,7 +74,6 @@ struct GemmParams {
     const uint8_t* mask;     // [M, N/8] or NULL
     float had_scale;
     int d_f32;
-    int dbg;
 };
 
 // ---------------------------------------------------------------------------
@@ -150,6 +155,7 @@ __device__ __forceinline__ uint32_t make_idesc(int n, uint32_t sf_id) {
 
 // Bounded wait on wall-clock time (2 s), for the pipeline barriers.
 __device__ __forceinline__ bool gemm_wait(uint64_t* bar, uint32_t parity, int32_t who, volatile int* dead) {
+    if (mbar_try_wait(bar, parity)) return true;
     if (*dead) return false;
     uint64_t t0 = 0;
     for (uint32_t i = 0;; ++i) {
@@ -164,6 +170,66 @@ __device__ __forceinline__ bool gemm_wait(uint64_t* bar, uint32_t parity, int32_
     atomicOr(&g_status, who | 0x100);
     *dead = 1;
     return false;
+}
+
+// Epilogue of one 32-row x 32-column block held as one accumulator row per thread: scale, optional
+// mask + un-rotation (the 32 columns are exactly one Hadamard group), convert, stage 32 rows x 64
+// bytes in 64B-swizzled shared memory and hand them to TMA -- one store for bf16, two (16 columns
+// each) for fp32.  Two 2 KB staging buffers per warp alternate.
+__device__ __forceinline__ void epilogue_block(const uint32_t (&r)[32], const GemmParams& p, const CUtensorMap* tm_d,
+                                               int64_t row, int row0, int col, uint8_t* stg, uint32_t& n_stores, int lane) {
+    float v[32];
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) * p.alpha;
+    if (p.mask) {
+        const uint32_t m = *reinterpret_cast<const uint32_t*>(p.mask + row * (p.N >> 3) + (col >> 3));
+#pragma unroll
+        for (int i = 0; i < 32; ++i) v[i] = ((m >> i) & 1u) ? v[i] : 0.f;
+        wht32(v);
+#pragma unroll
+        for (int i = 0; i < 32; ++i) v[i] *= p.had_scale;
+    }
+    if (p.d_f32) {
+#pragma unroll
+        for (int hf = 0; hf < 2; ++hf, ++n_stores) {
+            uint8_t* buf = stg + (n_stores & 1) * 2048;
+            if (lane == 0) bulk_wait_read1();
+            __syncwarp();
+            uint8_t* dst = buf + lane * 64;
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+                *reinterpret_cast<float4*>(dst + ((j ^ ((lane >> 1) & 3)) << 4)) =
+                    make_float4(v[16 * hf + 4 * j], v[16 * hf + 4 * j + 1], v[16 * hf + 4 * j + 2], v[16 * hf + 4 * j + 3]);
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+                tma_store_2d(tm_d, col + 16 * hf, row0, buf);
+                bulk_commit();
+            }
+        }
+    } else {
+        uint8_t* buf = stg + (n_stores & 1) * 2048;
+        ++n_stores;
+        if (lane == 0) bulk_wait_read1();
+        __syncwarp();
+        uint8_t* dst = buf + lane * 64;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            uint32_t w[4];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                __nv_bfloat162 t = __floats2bfloat162_rn(v[8 * j + 2 * k], v[8 * j + 2 * k + 1]);
+                w[k] = *reinterpret_cast<uint32_t*>(&t);
+            }
+            *reinterpret_cast<uint4*>(dst + ((j ^ ((lane >> 1) & 3)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+        }
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+            tma_store_2d(tm_d, col, row0, buf);
+            bulk_commit();
+        }
+    }
 }
 
 template <int BN>
@@ -232,7 +298,6 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_mxfp4_kernel(const __gri
                     const int s = it % C::STAGES;
                     const uint32_t ph = (it / C::STAGES) & 1;
                     if (!gemm_wait(&empty[s], ph ^ 1, WAIT_GEMM_EMPTY, dead)) break;
-                    TRACE(0, it);
                     const int nch = min(2, p.k_chunks - 2 * ks);
                     mbar_arrive_expect_tx(&full[s], C::A_BYTES + C::B_BYTES + nch * 512 * (1 + n_blocks));
                     tma_load_2d(s_a + s * C::A_BYTES, &tm_a, ks * BK_BYTES, m0, &full[s]);
@@ -260,15 +325,13 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_mxfp4_kernel(const __gri
                     const int s = it % C::STAGES;
                     const uint32_t ph = (it / C::STAGES) & 1;
                     if (!gemm_wait(&full[s], ph, WAIT_GEMM_FULL, dead)) break;
-                    TRACE(1, it);
                     if (!gemm_wait(&sf_full[s], ph, WAIT_GEMM_SF, dead)) break;
-                    TRACE(2, it);
                     tc_fence_after();
                     const int nch = min(2, p.k_chunks - 2 * ks);
                     const uint32_t sf_tmem = tmem_base + C::SF_COL0 + s * C::SF_COLS;
                     const uint64_t adesc = make_desc_sw128(smem_u32(s_a + s * C::A_BYTES));
                     const uint64_t bdesc = make_desc_sw128(smem_u32(s_b + s * C::B_BYTES));
-                    for (int c = 0; c < nch && !(p.dbg & 2); ++c) {
+                    for (int c = 0; c < nch; ++c) {
 #pragma unroll
                         for (int j = 0; j < 2; ++j) {
                             const uint32_t koff = (uint32_t)((c * 2 + j) * 32) >> 4;  // 64 elements = 32 bytes
@@ -279,7 +342,6 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_mxfp4_kernel(const __gri
                         }
                     }
                     tc_commit(&empty[s]);  // frees the stage once the MMAs above have read it
-                    TRACE(3, it);
                 }
                 tc_commit(&acc_full[as]);  // accumulator complete
             }
@@ -298,12 +360,11 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_mxfp4_kernel(const __gri
                 const int s = it % C::STAGES;
                 const uint32_t ph = (it / C::STAGES) & 1;
                 if (!gemm_wait(&full[s], ph, WAIT_GEMM_FULL, dead)) break;
-                if (warp == 6 && lane == 0) TRACE(4, it);
                 const int nch = min(2, p.k_chunks - 2 * ks);
                 const uint32_t sf_tmem = tmem_base + lane_base + C::SF_COL0 + s * C::SF_COLS;
                 const uint8_t* sfa = s_sfa + s * C::SFA_BYTES + lane * 16;
                 const uint8_t* sfb = s_sfb + s * C::SFB_BYTES + lane * 16;
-                for (int c = 0; c < nch && !(p.dbg & 4); ++c) {
+                for (int c = 0; c < nch; ++c) {
                     uint32_t r[8];
                     const uint4 va = *reinterpret_cast<const uint4*>(sfa + c * 512);
                     r[0] = va.x, r[1] = va.y, r[2] = va.z, r[3] = va.w;
@@ -322,7 +383,6 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_mxfp4_kernel(const __gri
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&sf_full[s]);
-                if (warp == 6 && lane == 0) TRACE(5, it);
             }
         }
     } else {
@@ -340,59 +400,11 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_mxfp4_kernel(const __gri
             const int row0 = m_blk * BM + q * 32;
             const int64_t row = (int64_t)row0 + lane;
             const int n_chunks = min(BN, p.N - n0) / 32;
-            for (int ch = 0; ch < n_chunks && !(p.dbg & 8); ++ch, ++n_stores) {
+            for (int ch = 0; ch < n_chunks; ++ch) {
                 uint32_t r[32];
                 tc_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + C::ACC_COL0 + as * BN + ch * 32, r);
                 tc_wait_ld();
-                float v[32];
-#pragma unroll
-                for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) * p.alpha;
-                const int col = n0 + ch * 32;
-                if (p.mask) {
-                    const uint32_t m = *reinterpret_cast<const uint32_t*>(p.mask + row * (p.N >> 3) + (col >> 3));
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) v[i] = ((m >> i) & 1u) ? v[i] : 0.f;
-                    wht32(v);
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) v[i] *= p.had_scale;
-                }
-                // stage the 32 x 32 block in (swizzled) shared memory and hand it to TMA
-                if (p.d_f32) {
-                    if (lane == 0) bulk_wait_read0();
-                    __syncwarp();
-                    uint8_t* dst = stg + lane * 128;
-#pragma unroll
-                    for (int j = 0; j < 8; ++j)
-                        *reinterpret_cast<float4*>(dst + ((j ^ (lane & 7)) << 4)) =
-                            make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
-                    fence_proxy_async_smem();
-                    __syncwarp();
-                    if (lane == 0) {
-                        tma_store_2d(&tm_d, col, row0, stg);
-                        bulk_commit();
-                    }
-                } else {
-                    uint8_t* buf = stg + (n_stores & 1) * 2048;
-                    if (lane == 0) bulk_wait_read1();
-                    __syncwarp();
-                    uint8_t* dst = buf + lane * 64;
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        uint32_t w[4];
-#pragma unroll
-                        for (int k = 0; k < 4; ++k) {
-                            __nv_bfloat162 t = __floats2bfloat162_rn(v[8 * j + 2 * k], v[8 * j + 2 * k + 1]);
-                            w[k] = *reinterpret_cast<uint32_t*>(&t);
-                        }
-                        *reinterpret_cast<uint4*>(dst + ((j ^ ((lane >> 1) & 3)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
-                    }
-                    fence_proxy_async_smem();
-                    __syncwarp();
-                    if (lane == 0) {
-                        tma_store_2d(&tm_d, col, row0, buf);
-                        bulk_commit();
-                    }
-                }
+                epilogue_block(r, p, &tm_d, row, row0, n0 + ch * 32, stg, n_stores, lane);
             }
             tc_fence_before();
             __syncwarp();
@@ -427,24 +439,39 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_mxfp4_kernel(const __gri
 // ===========================================================================================
 template <int BN>
 struct Gemm2Cfg {
-    static constexpr int STAGES = 5;
+    static constexpr int NSEG = BN / 32;                     // 32-row segments of B = scale columns per K-chunk
+    static constexpr int SFB_ST = NSEG <= 4 ? 4 : 8;         // columns written per tcgen05.st
+    static constexpr int SF_COLS = 8 + 2 * SFB_ST;           // SFA 2 x 4, SFB 2 x SFB_ST columns per stage
+    static constexpr int ACC_STAGES = (2 * BN + 2 * SF_COLS <= 512) ? 2 : 1;
+    static constexpr int SF_SLOTS = (512 - ACC_STAGES * BN) / SF_COLS >= 4 ? 4 : 2;
+    static constexpr int SF_COL0 = ACC_STAGES * BN;
+    static constexpr int TMEM_COLS = 512;
     static constexpr int A_BYTES = BM * BK_BYTES;            // 16 KB
     static constexpr int B_BYTES = (BN / 2) * BK_BYTES;      // this CTA's half of the B tile
     static constexpr int SFA_BYTES = 1024;
-    static constexpr int SFB_BLOCKS = BN / 128;
+    static constexpr int SFB_BLOCKS = (BN % 128 == 0) ? BN / 128 : BN / 128 + 2;  // 128-row scale blocks a tile can touch
     static constexpr int SFB_BYTES = SFB_BLOCKS * 1024;
     static constexpr int STAGE_BYTES = A_BYTES + B_BYTES + SFA_BYTES + SFB_BYTES;
-    static constexpr int NSEG = BN / 32;
-    static constexpr int SFB_ST = NSEG <= 4 ? 4 : 8;
-    static constexpr int SF_COLS = 8 + 2 * SFB_ST;
-    static constexpr int SF_COL0 = BN;
-    static constexpr int TMEM_COLS = 512;
-    static constexpr int STG_BYTES = 4 * 4096;
+    static constexpr int STG_BYTES = 4 * 4096;               // epilogue staging: 2 x 2 KB per epilogue warp
+    static constexpr int STAGES = (232448 - STG_BYTES - 512 - 1024) / STAGE_BYTES;
     static constexpr int SMEM = STAGES * STAGE_BYTES + STG_BYTES + 512 + 1024;
-    static_assert(SF_COL0 + STAGES * SF_COLS <= TMEM_COLS, "tensor memory budget");
-    static_assert(SMEM <= 232448, "shared memory budget");
+    static_assert(SF_COL0 + SF_SLOTS * SF_COLS <= TMEM_COLS, "tensor memory budget");
+    static_assert(SF_SLOTS < STAGES, "scale slots are recycled through the stage barriers");
+    static_assert(B_BYTES % 1024 == 0, "operand stages stay 1024-byte aligned");
 };
 
+// One lane of a fully converged warp (elect.sync): the issuing warp runs its loop on all 32 lanes so
+// that ring indices, descriptors and addresses stay warp-uniform, and only the tcgen05 instructions
+// themselves are predicated on the elected lane.
+__device__ __forceinline__ bool elect_one() {
+    uint32_t pred = 0;
+    asm volatile(
+        "{\n\t.reg .b32 rx;\n\t.reg .pred px;\n\t"
+        "elect.sync rx|px, 0xFFFFFFFF;\n\t"
+        "selp.u32 %0, 1, 0, px;\n\t}"
+        : "=r"(pred));
+    return pred != 0;
+}
 __device__ __forceinline__ uint32_t cluster_ctarank() {
     uint32_t r;
     asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
@@ -462,44 +489,6 @@ __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
 }
 __device__ __forceinline__ void cluster_sync_all() {
     asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait_cluster(uint64_t* bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.b32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok)
-        : "r"(smem_u32(bar)), "r"(parity)
-        : "memory");
-    return ok != 0;
-}
-__device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.b32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok)
-        : "r"(smem_u32(bar)), "r"(parity)
-        : "memory");
-    return ok != 0;
-}
-__device__ __forceinline__ bool gemm_wait_cluster(uint64_t* bar, uint32_t parity, int32_t who, volatile int* dead, bool plain = false) {
-    if (*dead) return false;
-    uint64_t t0 = 0;
-    for (uint32_t i = 0;; ++i) {
-        if (plain ? mbar_test_wait(bar, parity) : mbar_try_wait_cluster(bar, parity)) return true;
-        if ((i & 1023u) == 1023u) {
-            uint64_t now;
-            asm volatile("mov.u64 %0, %globaltimer;" : "=l"(now));
-            if (t0 == 0) t0 = now;
-            if (now - t0 > 2000000000ull || *dead) break;
-        }
-    }
-    atomicOr(&g_status, who | 0x200);
-    *dead = 1;
-    return false;
 }
 __device__ __forceinline__ void tmem_alloc2(uint32_t* dst_smem, uint32_t ncols) {
     asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(dst_smem)), "r"(ncols)
@@ -550,12 +539,12 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
     uint8_t* s_sfa = s_stg + C::STG_BYTES;
     uint8_t* s_sfb = s_sfa + C::STAGES * C::SFA_BYTES;
     uint64_t* bars = reinterpret_cast<uint64_t*>(s_sfb + C::STAGES * C::SFB_BYTES);
-    uint64_t* full = bars;                      // local: this CTA's copies of a stage have landed
-    uint64_t* empty = full + C::STAGES;         // local: the pair's MMAs are done with the stage
-    uint64_t* sf_full = empty + C::STAGES;      // leader only: 8 feeder warps (both CTAs) have fed the stage
-    uint64_t* acc_full = sf_full + C::STAGES;   // local: accumulator complete
-    uint64_t* acc_empty = acc_full + 1;         // leader only: 8 epilogue warps (both CTAs) have drained it
-    uint32_t* s_tmem = reinterpret_cast<uint32_t*>(acc_empty + 1);
+    uint64_t* full = bars;                            // local: this CTA's copies of a stage have landed
+    uint64_t* empty = full + C::STAGES;               // local: the pair's MMAs are done with the stage
+    uint64_t* sf_full = empty + C::STAGES;            // leader only: 8 feeder warps (both CTAs) have fed the stage
+    uint64_t* acc_full = sf_full + C::STAGES;         // local: accumulator complete
+    uint64_t* acc_empty = acc_full + C::ACC_STAGES;   // leader only: 8 epilogue warps (both CTAs) have drained it
+    uint32_t* s_tmem = reinterpret_cast<uint32_t*>(acc_empty + C::ACC_STAGES);
     volatile int* dead = reinterpret_cast<volatile int*>(s_tmem + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -568,8 +557,10 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
             mbar_init(&empty[i], 1);
             mbar_init(&sf_full[i], 8);
         }
-        mbar_init(acc_full, 1);
-        mbar_init(acc_empty, 8);
+        for (int i = 0; i < C::ACC_STAGES; ++i) {
+            mbar_init(&acc_full[i], 1);
+            mbar_init(&acc_empty[i], 8);
+        }
         *dead = 0;
         fence_mbar_init();
         prefetch_tmap(&tm_a);
@@ -607,7 +598,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
                     const uint32_t ph = (it / C::STAGES) & 1;
                     if (!gemm_wait(&empty[s], ph ^ 1, WAIT_GEMM_EMPTY, dead)) break;
                     TRACE(0, it);
-                    TRACE1(6, it);
+                    TRACE_PEER(6, it);
                     const int nch = min(2, p.k_chunks - 2 * ks);
                     mbar_arrive_expect_tx(&full[s], C::A_BYTES + C::B_BYTES + nch * 512 * (1 + n_blocks));
                     tma_load_2d(s_a + s * C::A_BYTES, &tm_a, ks * BK_BYTES, m0, &full[s]);
@@ -623,60 +614,54 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
         }
     } else if (warp == 1) {
         // ------------------------------ MMA issuer (leader CTA only) ------------------------------
-        if (leader && lane == 0) {
-            uint32_t it = 0, acc_it = 0;
-            uint32_t empty_peer[C::STAGES];
-#pragma unroll
-            for (int i = 0; i < C::STAGES; ++i) empty_peer[i] = mapa_u32(smem_u32(&empty[i]), 1);
-            const uint32_t acc_full_peer = mapa_u32(smem_u32(acc_full), 1);
-            for (int tile = cluster_id; tile < n_tiles_total && !*dead; tile += n_clusters, ++acc_it) {
-                if (!gemm_wait_cluster(acc_empty, (acc_it & 1) ^ 1, WAIT_GEMM_ACC_EMPTY, dead)) break;
+        if (leader) {
+            // ring positions are kept as (index, phase) pairs: no division in the issue loop
+            uint32_t s = 0, ph = 0, slot = 0, as = 0, aph = 0;
+            const uint32_t idesc0 = make_idesc2(BN, 0), idesc1 = make_idesc2(BN, 2);
+            const uint32_t a_base = smem_u32(s_a), b_base = smem_u32(s_b);
+            const uint32_t empty_own = smem_u32(&empty[0]), empty_peer = mapa_u32(smem_u32(&empty[0]), 1);
+            const uint32_t accf_own = smem_u32(&acc_full[0]), accf_peer = mapa_u32(smem_u32(&acc_full[0]), 1);
+            for (int tile = cluster_id; tile < n_tiles_total && !*dead; tile += n_clusters) {
+                if (!gemm_wait(&acc_empty[as], aph ^ 1, WAIT_GEMM_ACC_EMPTY, dead)) break;
                 tc_fence_after();
-                const uint32_t d_tmem = tmem_base;
-                for (int ks = 0; ks < k_stages; ++ks, ++it) {
-                    const int s = it % C::STAGES;
-                    const uint32_t ph = (it / C::STAGES) & 1;
-                    if (!gemm_wait(&full[s], ph, WAIT_GEMM_FULL, dead)) break;
-                    TRACE(1, it);
-                    if (!gemm_wait_cluster(&sf_full[s], ph, WAIT_GEMM_SF, dead)) break;
-                    TRACE(2, it);
+                const uint32_t d_tmem = tmem_base + as * BN;
+                for (int ks = 0; ks < k_stages; ++ks) {
+                    // the feeders arrive only after the stage's copies have landed in BOTH CTAs, so this
+                    // one barrier covers operands and scales
+                    if (!gemm_wait(&sf_full[s], ph, WAIT_GEMM_SF, dead)) break;
                     tc_fence_after();
                     const int nch = min(2, p.k_chunks - 2 * ks);
-                    const uint32_t sf_tmem = tmem_base + C::SF_COL0 + s * C::SF_COLS;
-                    const uint64_t adesc = make_desc_sw128(smem_u32(s_a + s * C::A_BYTES));
-                    const uint64_t bdesc = make_desc_sw128(smem_u32(s_b + s * C::B_BYTES));
-                    for (int c = 0; c < nch && !(p.dbg & 2); ++c) {
-#pragma unroll
-                        for (int j = 0; j < 2; ++j) {
-                            const uint32_t koff = (uint32_t)((c * 2 + j) * 32) >> 4;
-                            const uint32_t sfid = (uint32_t)j * 2u;
-                            tc_mma2_mxf4(d_tmem, adesc + koff, bdesc + koff, make_idesc2(BN, sfid),
-                                         (sf_tmem + c * 4) | (sfid << 30), (sf_tmem + 8 + c * C::SFB_ST) | (sfid << 30),
-                                         (ks | c | j) != 0);
-                            TRACE(8 + c * 2 + j, it);
+                    const uint32_t sf_tmem = tmem_base + C::SF_COL0 + slot * C::SF_COLS;
+                    const uint64_t adesc = make_desc_sw128(a_base + s * C::A_BYTES);
+                    const uint64_t bdesc = make_desc_sw128(b_base + s * C::B_BYTES);
+                    if (elect_one()) {
+                        tc_mma2_mxf4(d_tmem, adesc, bdesc, idesc0, sf_tmem, sf_tmem + 8, ks != 0);
+                        tc_mma2_mxf4(d_tmem, adesc + 2, bdesc + 2, idesc1, sf_tmem | (2u << 30), (sf_tmem + 8) | (2u << 30), 1);
+                        if (nch == 2) {
+                            tc_mma2_mxf4(d_tmem, adesc + 4, bdesc + 4, idesc0, sf_tmem + 4, sf_tmem + 8 + C::SFB_ST, 1);
+                            tc_mma2_mxf4(d_tmem, adesc + 6, bdesc + 6, idesc1, (sf_tmem + 4) | (2u << 30),
+                                         (sf_tmem + 8 + C::SFB_ST) | (2u << 30), 1);
                         }
+                        // one completion event, signalled to both CTAs: frees the operand stage and the scale slot
+                        tc_commit2(empty_own + s * 8);
+                        tc_commit2(empty_peer + s * 8);
                     }
-                    if ((p.dbg & 2) && (p.dbg & 128)) {  // no MMAs were issued: plain arrives are equivalent
-                        mbar_arrive(&empty[s]);
-                        mbar_arrive_cluster(empty_peer[s]);
-                    } else {
-                        tc_commit2(smem_u32(&empty[s]));
-                        TRACE(12, it);
-                        tc_commit2(empty_peer[s]);
-                    }
-                    TRACE(3, it);
+                    __syncwarp();
+                    if (++s == C::STAGES) s = 0, ph ^= 1;
+                    if (++slot == C::SF_SLOTS) slot = 0;
                 }
-                tc_commit2(smem_u32(acc_full));
-                tc_commit2(acc_full_peer);
+                if (elect_one()) {
+                    tc_commit2(accf_own + as * 8);
+                    tc_commit2(accf_peer + as * 8);
+                }
+                __syncwarp();
+                if (++as == C::ACC_STAGES) as = 0, aph ^= 1;
             }
         }
     } else if (warp >= 6) {
         // ------------------------------ scale feeders (both CTAs) ------------------------------
         const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
         uint32_t it = 0;
-        uint32_t sf_full_leader[C::STAGES];
-#pragma unroll
-        for (int i = 0; i < C::STAGES; ++i) sf_full_leader[i] = mapa_u32(smem_u32(&sf_full[i]), 0);
         for (int tile = cluster_id; tile < n_tiles_total && !*dead; tile += n_clusters) {
             const int n0 = (tile / m_pairs) * BN;
             const int seg0 = (n0 % 128) / 32;
@@ -684,12 +669,19 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
                 const int s = it % C::STAGES;
                 const uint32_t ph = (it / C::STAGES) & 1;
                 if (!gemm_wait(&full[s], ph, WAIT_GEMM_FULL, dead)) break;
-                if (warp == 6 && lane == 0) { TRACE(4, it); TRACE1(7, it); }
+                if (warp == 6 && lane == 0) { TRACE(4, it); TRACE_PEER(7, it); }
+                // the scale slot was last read by the MMAs of iteration it - SF_SLOTS; their completion is
+                // what the `empty` barrier of that iteration's operand stage reports
+                if (it >= (uint32_t)C::SF_SLOTS) {
+                    const uint32_t pit = it - C::SF_SLOTS;
+                    if (!gemm_wait(&empty[pit % C::STAGES], (pit / C::STAGES) & 1, WAIT_GEMM_EMPTY, dead)) break;
+                    tc_fence_after();
+                }
                 const int nch = min(2, p.k_chunks - 2 * ks);
-                const uint32_t sf_tmem = tmem_base + lane_base + C::SF_COL0 + s * C::SF_COLS;
+                const uint32_t sf_tmem = tmem_base + lane_base + C::SF_COL0 + (it % C::SF_SLOTS) * C::SF_COLS;
                 const uint8_t* sfa = s_sfa + s * C::SFA_BYTES + lane * 16;
                 const uint8_t* sfb = s_sfb + s * C::SFB_BYTES + lane * 16;
-                for (int c = 0; c < nch && !(p.dbg & 4); ++c) {
+                for (int c = 0; c < nch; ++c) {
                     uint32_t r[8];
                     const uint4 va = *reinterpret_cast<const uint4*>(sfa + c * 512);
                     r[0] = va.x, r[1] = va.y, r[2] = va.z, r[3] = va.w;
@@ -704,85 +696,38 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
                     else
                         tc_st8(sf_tmem + 8 + c * C::SFB_ST, r);
                 }
-                if (warp == 6 && lane == 0) TRACE(13, it);
                 tc_wait_st();
-                if (warp == 6 && lane == 0) TRACE(14, it);
                 tc_fence_before();
                 __syncwarp();
-                if (lane == 0) mbar_arrive_cluster(sf_full_leader[s]);
-                if (warp == 6 && lane == 0) TRACE(5, it);
+                if (lane == 0) mbar_arrive_cluster(mapa_u32(smem_u32(&sf_full[s]), 0));
+                if (warp == 6 && lane == 0) { TRACE(5, it); TRACE_PEER(8, it); }
             }
         }
     } else {
         // ------------------------------ epilogue (both CTAs) ------------------------------
         const int q = warp & 3;
         uint8_t* stg = s_stg + (warp - 2) * 4096;
-        const uint32_t acc_empty_leader = mapa_u32(smem_u32(acc_empty), 0);
         uint32_t acc_it = 0, n_stores = 0;
         for (int tile = cluster_id; tile < n_tiles_total && !*dead; tile += n_clusters, ++acc_it) {
             const int m_blk = (tile % m_pairs) * 2 + (int)rank, n_blk = tile / m_pairs;
             const int n0 = n_blk * BN;
-            if (!gemm_wait(acc_full, acc_it & 1, WAIT_GEMM_ACC_FULL, dead)) break;
+            const int as = acc_it % C::ACC_STAGES;
+            if (!gemm_wait(&acc_full[as], (acc_it / C::ACC_STAGES) & 1, WAIT_GEMM_ACC_FULL, dead)) break;
+            if (warp == 2 && lane == 0) TRACE(9, acc_it);
             tc_fence_after();
             const int row0 = m_blk * BM + q * 32;
             const int64_t row = (int64_t)row0 + lane;
             const int n_chunks = min(BN, p.N - n0) / 32;
-            for (int ch = 0; ch < n_chunks && !(p.dbg & 8); ++ch, ++n_stores) {
+            for (int ch = 0; ch < n_chunks; ++ch) {
                 uint32_t r[32];
-                tc_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + ch * 32, r);
+                tc_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + as * BN + ch * 32, r);
                 tc_wait_ld();
-                float v[32];
-#pragma unroll
-                for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) * p.alpha;
-                const int col = n0 + ch * 32;
-                if (p.mask) {
-                    const uint32_t m = *reinterpret_cast<const uint32_t*>(p.mask + row * (p.N >> 3) + (col >> 3));
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) v[i] = ((m >> i) & 1u) ? v[i] : 0.f;
-                    wht32(v);
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) v[i] *= p.had_scale;
-                }
-                if (p.d_f32) {
-                    if (lane == 0) bulk_wait_read0();
-                    __syncwarp();
-                    uint8_t* dst = stg + lane * 128;
-#pragma unroll
-                    for (int j = 0; j < 8; ++j)
-                        *reinterpret_cast<float4*>(dst + ((j ^ (lane & 7)) << 4)) =
-                            make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
-                    fence_proxy_async_smem();
-                    __syncwarp();
-                    if (lane == 0) {
-                        tma_store_2d(&tm_d, col, row0, stg);
-                        bulk_commit();
-                    }
-                } else {
-                    uint8_t* buf = stg + (n_stores & 1) * 2048;
-                    if (lane == 0) bulk_wait_read1();
-                    __syncwarp();
-                    uint8_t* dst = buf + lane * 64;
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        uint32_t w[4];
-#pragma unroll
-                        for (int k = 0; k < 4; ++k) {
-                            __nv_bfloat162 t = __floats2bfloat162_rn(v[8 * j + 2 * k], v[8 * j + 2 * k + 1]);
-                            w[k] = *reinterpret_cast<uint32_t*>(&t);
-                        }
-                        *reinterpret_cast<uint4*>(dst + ((j ^ ((lane >> 1) & 3)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
-                    }
-                    fence_proxy_async_smem();
-                    __syncwarp();
-                    if (lane == 0) {
-                        tma_store_2d(&tm_d, col, row0, buf);
-                        bulk_commit();
-                    }
-                }
+                epilogue_block(r, p, &tm_d, row, row0, n0 + ch * 32, stg, n_stores, lane);
             }
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive_cluster(acc_empty_leader);
+            if (lane == 0) mbar_arrive_cluster(mapa_u32(smem_u32(&acc_empty[as]), 0));
+            if (warp == 2 && lane == 0) TRACE(10, acc_it);
         }
         if (lane == 0) bulk_wait0();
     }
@@ -812,7 +757,7 @@ static int launch_gemm_2cta(const uint8_t* a, const uint8_t* b, void* d, const G
     rc = make_tmap_2d(&tm_b, b, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, p.K / 2, p.N, p.K / 2, BK_BYTES, BN / 2, 3);
     if (rc) return rc;
     if (p.d_f32)
-        rc = make_tmap_2d(&tm_d, d, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, p.N, p.M, (uint64_t)p.N * 4, 32, 32, 3);
+        rc = make_tmap_2d(&tm_d, d, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, p.N, p.M, (uint64_t)p.N * 4, 16, 32, 2);
     else
         rc = make_tmap_2d(&tm_d, d, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, p.N, p.M, (uint64_t)p.N * 2, 32, 32, 2);
     if (rc) return rc;
@@ -843,6 +788,22 @@ static int launch_gemm_2cta(const uint8_t* a, const uint8_t* b, void* d, const G
     const int pair_tiles = (p.m_tiles / 2) * p.n_tiles;
     const int clusters = pair_tiles < cached_clusters ? pair_tiles : cached_clusters;
     kern<<<clusters * 2, GEMM_THREADS, C::SMEM, stream>>>(tm_a, tm_b, tm_d, p);
+#ifdef QUARTET_GEMM_TRACE
+    {
+        static long long h[16][64];
+        cudaDeviceSynchronize();
+        if (cudaMemcpyFromSymbol(h, g_trace, sizeof(h)) == cudaSuccess) {
+            const char* names[9] = {"prod:empty_ok", "mma:full_ok", "mma:sf_ok", "mma:commit", "feed:full_ok", "feed:arrive",
+                                    "PEER prod:empty_ok", "PEER feed:full_ok", "PEER feed:arrive"};
+            for (int i = 0; i < 48; ++i) {
+                fprintf(stderr, "it %2d", i);
+                for (int k = 0; k < 9; ++k) fprintf(stderr, "  %s=%6lld", names[k], h[k][i] - (k < 6 ? h[0][0] : h[6][0]));
+                fprintf(stderr, "\n");
+            }
+            for (int i = 0; i < 4; ++i) fprintf(stderr, "tile %d epi:acc_full_ok=%lld epi:done=%lld\n", i, h[9][i] - h[0][0], h[10][i] - h[0][0]);
+        }
+    }
+#endif
     return check_cuda(cudaGetLastError(), "gemm (2-CTA) launch");
 }
 
@@ -857,7 +818,7 @@ static int launch_gemm(const uint8_t* a, const uint8_t* b, void* d, const GemmPa
     rc = make_tmap_2d(&tm_b, b, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, p.K / 2, p.N, p.K / 2, BK_BYTES, p.N < BN ? p.N : BN, 3);
     if (rc) return rc;
     if (p.d_f32)
-        rc = make_tmap_2d(&tm_d, d, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, p.N, p.M, (uint64_t)p.N * 4, 32, 32, 3);
+        rc = make_tmap_2d(&tm_d, d, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, p.N, p.M, (uint64_t)p.N * 4, 16, 32, 2);
     else
         rc = make_tmap_2d(&tm_d, d, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, p.N, p.M, (uint64_t)p.N * 2, 32, 32, 2);
     if (rc) return rc;
@@ -874,20 +835,6 @@ static int launch_gemm(const uint8_t* a, const uint8_t* b, void* d, const GemmPa
 }
 
 QUARTET_DEFINE_STATUS_READER(status_gemm)
-
-void dump_gemm_trace() {
-    static long long h[16][64];
-    cudaDeviceSynchronize();
-    if (cudaMemcpyFromSymbol(h, g_trace, sizeof(h)) != cudaSuccess) return;
-    const char* names[8] = {"prod:empty_ok", "mma:full_ok", "mma:sf_ok", "mma:commit", "feed:full_ok", "feed:arrive", "PEER prod:empty_ok", "PEER feed:full_ok"};
-    long long t0 = h[0][0], t1 = h[6][0];
-    for (int i = 0; i < 40; ++i) {
-        fprintf(stderr, "it %2d", i);
-        for (int k = 0; k < 8; ++k) fprintf(stderr, "  %s=%6lld", names[k], h[k][i] - (k < 6 ? t0 : t1));
-        fprintf(stderr, "\n      mma issue +%lld +%lld +%lld +%lld commit1 +%lld commit2 +%lld | feeder st-issued +%lld wait_st +%lld arrive +%lld", h[8][i] - h[2][i], h[9][i] - h[2][i], h[10][i] - h[2][i], h[11][i] - h[2][i], h[12][i] - h[2][i], h[3][i] - h[2][i], h[13][i] - h[4][i], h[14][i] - h[4][i], h[5][i] - h[4][i]);
-        fprintf(stderr, "\n");
-    }
-}
 
 }  // namespace quartet
 
@@ -915,8 +862,6 @@ extern "C" __attribute__((visibility("default"))) int quartet_gemm_mxfp4_tn(cons
     p.m_tiles = (int)(M / BM);
     p.alpha = alpha, p.mask = mask, p.had_scale = had_scale;
     p.d_f32 = d_dtype == QUARTET_F32;
-    static const int dbg = [] { const char* e = getenv("QUARTET_GEMM_DEBUG"); return e ? atoi(e) : 0; }();
-    p.dbg = dbg;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     // Tile width: 256 unless the output is narrow or not a multiple of 256.  QUARTET_GEMM_BN=128|256
     // overrides the choice (tuning aid).
@@ -932,14 +877,9 @@ extern "C" __attribute__((visibility("default"))) int quartet_gemm_mxfp4_tn(cons
     // CTA pairs need an even number of 128-row tiles; QUARTET_GEMM_CTAS=1|2 overrides (tuning aid).
     const bool pair = forced_cta ? forced_cta == 2 : true;
     if (pair && wide && M % 256 == 0) {
-        int r = launch_gemm_2cta<256>(a, b, d, p, s);
-        if (p.dbg & 256) dump_gemm_trace();
-        return r;
+        if (forced_bn == 256) return launch_gemm_2cta<256>(a, b, d, p, s);
+        return launch_gemm_2cta<224>(a, b, d, p, s);
     }
-    if (wide) {
-        int r = launch_gemm<256>(a, b, d, p, s);
-        if (p.dbg & 256) dump_gemm_trace();
-        return r;
-    }
+    if (wide) return launch_gemm<256>(a, b, d, p, s);
     return launch_gemm<128>(a, b, d, p, s);
 }
