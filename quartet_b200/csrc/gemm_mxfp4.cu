@@ -628,12 +628,15 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
                 for (int ks = 0; ks < k_stages; ++ks) {
                     // the feeders arrive only after the stage's copies have landed in BOTH CTAs, so this
                     // one barrier covers operands and scales
+                    TRACE(1, tile == cluster_id ? ks : 32 + ks);
                     if (!gemm_wait(&sf_full[s], ph, WAIT_GEMM_SF, dead)) break;
+                    TRACE(2, tile == cluster_id ? ks : 32 + ks);
                     tc_fence_after();
                     const int nch = min(2, p.k_chunks - 2 * ks);
                     const uint32_t sf_tmem = tmem_base + C::SF_COL0 + slot * C::SF_COLS;
                     const uint64_t adesc = make_desc_sw128(a_base + s * C::A_BYTES);
                     const uint64_t bdesc = make_desc_sw128(b_base + s * C::B_BYTES);
+                    TRACE(11, tile == cluster_id ? ks : 32 + ks);
                     if (elect_one()) {
                         tc_mma2_mxf4(d_tmem, adesc, bdesc, idesc0, sf_tmem, sf_tmem + 8, ks != 0);
                         tc_mma2_mxf4(d_tmem, adesc + 2, bdesc + 2, idesc1, sf_tmem | (2u << 30), (sf_tmem + 8) | (2u << 30), 1);
@@ -642,11 +645,13 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
                             tc_mma2_mxf4(d_tmem, adesc + 6, bdesc + 6, idesc1, (sf_tmem + 4) | (2u << 30),
                                          (sf_tmem + 8 + C::SFB_ST) | (2u << 30), 1);
                         }
+                        TRACE(12, tile == cluster_id ? ks : 32 + ks);
                         // one completion event, signalled to both CTAs: frees the operand stage and the scale slot
                         tc_commit2(empty_own + s * 8);
                         tc_commit2(empty_peer + s * 8);
                     }
                     __syncwarp();
+                    TRACE(3, tile == cluster_id ? ks : 32 + ks);
                     if (++s == C::STAGES) s = 0, ph ^= 1;
                     if (++slot == C::SF_SLOTS) slot = 0;
                 }
@@ -670,6 +675,24 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
                 const uint32_t ph = (it / C::STAGES) & 1;
                 if (!gemm_wait(&full[s], ph, WAIT_GEMM_FULL, dead)) break;
                 if (warp == 6 && lane == 0) { TRACE(4, it); TRACE_PEER(7, it); }
+                const int nch = min(2, p.k_chunks - 2 * ks);
+                const uint32_t sf_tmem = tmem_base + lane_base + C::SF_COL0 + (it % C::SF_SLOTS) * C::SF_COLS;
+                const uint8_t* sfa = s_sfa + s * C::SFA_BYTES + lane * 16;
+                const uint8_t* sfb = s_sfb + s * C::SFB_BYTES + lane * 16;
+                // shared -> registers first, so that only the tensor-memory stores remain once the slot is free
+                uint32_t ra[2][8], rb[2][8];
+#pragma unroll
+                for (int c = 0; c < 2; ++c) {
+                    const uint4 va = c < nch ? *reinterpret_cast<const uint4*>(sfa + c * 512) : make_uint4(0, 0, 0, 0);
+                    ra[c][0] = va.x, ra[c][1] = va.y, ra[c][2] = va.z, ra[c][3] = va.w;
+#pragma unroll
+                    for (int j = 0; j < C::SFB_ST; ++j) {
+                        const int seg = seg0 + j;
+                        rb[c][j] = (j < C::NSEG && c < nch)
+                                       ? *reinterpret_cast<const uint32_t*>(sfb + (seg >> 2) * 1024 + c * 512 + (seg & 3) * 4)
+                                       : 0u;
+                    }
+                }
                 // the scale slot was last read by the MMAs of iteration it - SF_SLOTS; their completion is
                 // what the `empty` barrier of that iteration's operand stage reports
                 if (it >= (uint32_t)C::SF_SLOTS) {
@@ -677,24 +700,15 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
                     if (!gemm_wait(&empty[pit % C::STAGES], (pit / C::STAGES) & 1, WAIT_GEMM_EMPTY, dead)) break;
                     tc_fence_after();
                 }
-                const int nch = min(2, p.k_chunks - 2 * ks);
-                const uint32_t sf_tmem = tmem_base + lane_base + C::SF_COL0 + (it % C::SF_SLOTS) * C::SF_COLS;
-                const uint8_t* sfa = s_sfa + s * C::SFA_BYTES + lane * 16;
-                const uint8_t* sfb = s_sfb + s * C::SFB_BYTES + lane * 16;
-                for (int c = 0; c < nch; ++c) {
-                    uint32_t r[8];
-                    const uint4 va = *reinterpret_cast<const uint4*>(sfa + c * 512);
-                    r[0] = va.x, r[1] = va.y, r[2] = va.z, r[3] = va.w;
-                    tc_st4(sf_tmem + c * 4, r);
 #pragma unroll
-                    for (int j = 0; j < C::SFB_ST; ++j) {
-                        const int seg = seg0 + j;
-                        r[j] = j < C::NSEG ? *reinterpret_cast<const uint32_t*>(sfb + (seg >> 2) * 1024 + c * 512 + (seg & 3) * 4) : 0u;
+                for (int c = 0; c < 2; ++c) {
+                    if (c < nch) {
+                        tc_st4(sf_tmem + c * 4, ra[c]);
+                        if (C::SFB_ST == 4)
+                            tc_st4(sf_tmem + 8 + c * C::SFB_ST, rb[c]);
+                        else
+                            tc_st8(sf_tmem + 8 + c * C::SFB_ST, rb[c]);
                     }
-                    if (C::SFB_ST == 4)
-                        tc_st4(sf_tmem + 8 + c * C::SFB_ST, r);
-                    else
-                        tc_st8(sf_tmem + 8 + c * C::SFB_ST, r);
                 }
                 tc_wait_st();
                 tc_fence_before();
@@ -795,11 +809,10 @@ static int launch_gemm_2cta(const uint8_t* a, const uint8_t* b, void* d, const G
         if (cudaMemcpyFromSymbol(h, g_trace, sizeof(h)) == cudaSuccess) {
             const char* names[9] = {"prod:empty_ok", "mma:full_ok", "mma:sf_ok", "mma:commit", "feed:full_ok", "feed:arrive",
                                     "PEER prod:empty_ok", "PEER feed:full_ok", "PEER feed:arrive"};
-            for (int i = 0; i < 48; ++i) {
-                fprintf(stderr, "it %2d", i);
-                for (int k = 0; k < 9; ++k) fprintf(stderr, "  %s=%6lld", names[k], h[k][i] - (k < 6 ? h[0][0] : h[6][0]));
-                fprintf(stderr, "\n");
-            }
+            for (int i = 0; i < 64; ++i)
+                fprintf(stderr, "it %2d loop_top=%6lld sf_ok=+%lld premma=+%lld mmas=+%lld commits=+%lld | prod_empty_ok=%6lld feed_full_ok=%6lld feed_arrive=%6lld\n", i,
+                        h[1][i] - h[0][0], h[2][i] - h[1][i], h[11][i] - h[2][i], h[12][i] - h[11][i], h[3][i] - h[12][i], h[0][i] - h[0][0],
+                        h[4][i] - h[0][0], h[5][i] - h[0][0]);
             for (int i = 0; i < 4; ++i) fprintf(stderr, "tile %d epi:acc_full_ok=%lld epi:done=%lld\n", i, h[9][i] - h[0][0], h[10][i] - h[0][0]);
         }
     }
@@ -863,7 +876,7 @@ extern "C" __attribute__((visibility("default"))) int quartet_gemm_mxfp4_tn(cons
     p.alpha = alpha, p.mask = mask, p.had_scale = had_scale;
     p.d_f32 = d_dtype == QUARTET_F32;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    // Tile width: 256 unless the output is narrow or not a multiple of 256.  QUARTET_GEMM_BN=128|256
+    // Tile width: 256 unless the output is narrow or not a multiple of 256.  QUARTET_GEMM_BN=128|224|256
     // overrides the choice (tuning aid).
     static const int forced_bn = [] {
         const char* e = getenv("QUARTET_GEMM_BN");
@@ -873,12 +886,14 @@ extern "C" __attribute__((visibility("default"))) int quartet_gemm_mxfp4_tn(cons
         const char* e = getenv("QUARTET_GEMM_CTAS");
         return e ? atoi(e) : 0;
     }();
-    const bool wide = forced_bn ? forced_bn == 256 : (N % 256 == 0 || N > 1024);
+    const bool wide = forced_bn ? forced_bn >= 224 : (N % 256 == 0 || N > 1024);
     // CTA pairs need an even number of 128-row tiles; QUARTET_GEMM_CTAS=1|2 overrides (tuning aid).
     const bool pair = forced_cta ? forced_cta == 2 : true;
     if (pair && wide && M % 256 == 0) {
-        if (forced_bn == 256) return launch_gemm_2cta<256>(a, b, d, p, s);
-        return launch_gemm_2cta<224>(a, b, d, p, s);
+        // 256-wide tiles with one accumulator measure faster than 224-wide double-buffered ones
+        // (the latter leave room for only two scale slots in tensor memory, which throttles the feeders)
+        if (forced_bn == 224) return launch_gemm_2cta<224>(a, b, d, p, s);
+        return launch_gemm_2cta<256>(a, b, d, p, s);
     }
     if (wide) return launch_gemm<256>(a, b, d, p, s);
     return launch_gemm<128>(a, b, d, p, s);
