@@ -45,7 +45,7 @@ constexpr int tile_smem_bytes() {
 }
 
 template <int SRC, int ROUND>
-__global__ void __launch_bounds__(TT_THREADS, 2) quant_tile_t_kernel(const __grid_constant__ CUtensorMap tm_in,
+__global__ void __launch_bounds__(TT_THREADS, 4) quant_tile_t_kernel(const __grid_constant__ CUtensorMap tm_in,
                                                                     const __grid_constant__ CUtensorMap tm_out,
                                                                     const TileTParams p) {
     extern __shared__ uint8_t smem_raw[];
@@ -90,60 +90,52 @@ __global__ void __launch_bounds__(TT_THREADS, 2) quant_tile_t_kernel(const __gri
 
     const int cp = tid & 63;   // source column pair within the tile
     const int rg = tid >> 6;   // group of 32 source rows within the tile
-    float a[32], b[32];        // columns 2cp and 2cp+1 over rows rg*32 .. rg*32+31
-
-    if (SRC == SRC_BF16) {
-        const uint8_t* base = s_in + (cp >> 5) * BOX_BYTES;
-        const int chunk = (cp & 31) >> 2, word = cp & 3;
-#pragma unroll
-        for (int i = 0; i < 32; ++i) {
-            const int r = rg * 32 + i;
-            const uint32_t v = *reinterpret_cast<const uint32_t*>(base + r * 128 + ((chunk ^ (r & 7)) << 4) + word * 4);
-            a[i] = __uint_as_float(v << 16);
-            b[i] = __uint_as_float(v & 0xFFFF0000u);
-        }
-    } else if (SRC == SRC_F32) {
-        const uint8_t* base = s_in + (cp >> 4) * BOX_BYTES;
-        const int chunk = (cp & 15) >> 1, half = cp & 1;
-#pragma unroll
-        for (int i = 0; i < 32; ++i) {
-            const int r = rg * 32 + i;
-            const float2 v = *reinterpret_cast<const float2*>(base + r * 128 + ((chunk ^ (r & 7)) << 4) + half * 8);
-            a[i] = v.x;
-            b[i] = v.y;
-        }
-    } else {
-        const uint8_t* s_sfin = s_in + TT * 64;
-        const int kb = cp >> 4;  // source scale block (32 source columns) of this column pair
-#pragma unroll
-        for (int i = 0; i < 32; ++i) {
-            const int r = rg * 32 + i;
-            const uint32_t byte = s_in[r * 64 + cp];
-            const uint32_t sfb = s_sfin[i * 16 + rg * 4 + kb];  // (r % 32) * 16 + (r / 32) * 4 + kb
-            const float sc = __uint_as_float(sfb << 23) * p.in_scale;
-            const float2 f = e2m1x2_to_float2(byte);
-            a[i] = f.x * sc;
-            b[i] = f.y * sc;
-        }
-    }
-
-    wht32(a);
-    wht32(b);
-
     const int64_t out_kb = (int64_t)(row0 >> 5) + rg;           // scale block along the output row
     const int64_t groups_per_out_row = p.rows >> 5;
-    uint32_t words[4];
-    int e8m0;
-#pragma unroll
+
+    // The two columns of the pair are processed one after the other (the second pass re-reads shared
+    // memory): 32 live values instead of 64 keeps the kernel at 64 registers, i.e. twice the warps per SM.
+#pragma unroll 1
     for (int c = 0; c < 2; ++c) {
+        float a[32];  // column 2cp + c over rows rg*32 .. rg*32+31
+        if (SRC == SRC_BF16) {
+            const uint8_t* base = s_in + (cp >> 5) * BOX_BYTES + c * 2;
+            const int chunk = (cp & 31) >> 2, word = cp & 3;
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+                const int r = rg * 32 + i;
+                const uint32_t v = *reinterpret_cast<const uint16_t*>(base + r * 128 + ((chunk ^ (r & 7)) << 4) + word * 4);
+                a[i] = __uint_as_float(v << 16);
+            }
+        } else if (SRC == SRC_F32) {
+            const uint8_t* base = s_in + (cp >> 4) * BOX_BYTES + c * 4;
+            const int chunk = (cp & 15) >> 1, half = cp & 1;
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+                const int r = rg * 32 + i;
+                a[i] = *reinterpret_cast<const float*>(base + r * 128 + ((chunk ^ (r & 7)) << 4) + half * 8);
+            }
+        } else {
+            const uint8_t* s_sfin = s_in + TT * 64;
+            const int kb = cp >> 4;  // source scale block (32 source columns) of this column pair
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+                const int r = rg * 32 + i;
+                const uint32_t byte = s_in[r * 64 + cp];
+                const uint32_t sfb = s_sfin[i * 16 + rg * 4 + kb];  // (r % 32) * 16 + (r / 32) * 4 + kb
+                const float sc = __uint_as_float(sfb << 23) * p.in_scale;
+                const float2 f = e2m1x2_to_float2(byte);
+                a[i] = (c ? f.y : f.x) * sc;
+            }
+        }
+        wht32(a);
         const int oc = 2 * cp + c;                               // output row within the tile
         const int64_t orow = (int64_t)col0 + oc;
         const uint64_t g = (uint64_t)orow * (uint64_t)groups_per_out_row + (uint64_t)out_kb;
         const int64_t flat = orow * p.rows + out_kb * 32;
-        if (c == 0)
-            absmax_quantize_group<ROUND>(a, p.had_scale, g, flat, true, p.seed, p.offset, p.noise, flip, words, e8m0);
-        else
-            absmax_quantize_group<ROUND>(b, p.had_scale, g, flat, true, p.seed, p.offset, p.noise, flip, words, e8m0);
+        uint32_t words[4];
+        int e8m0;
+        absmax_quantize_group<ROUND>(a, p.had_scale, g, flat, true, p.seed, p.offset, p.noise, flip, words, e8m0);
         *reinterpret_cast<uint4*>(s_codes + oc * 64 + rg * 16) = make_uint4(words[0], words[1], words[2], words[3]);
         s_sf[(oc & 31) * 16 + (oc >> 5) * 4 + rg] = (uint8_t)e8m0;
     }
