@@ -505,6 +505,14 @@ __device__ __forceinline__ void tc_commit2(uint32_t cluster_addr) {
     asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(cluster_addr)
                  : "memory");
 }
+// the same, arriving on the barrier at this shared-memory offset in BOTH CTAs of the pair (one
+// instruction instead of two commits; only the completion signal is multicast, no data copy)
+__device__ __forceinline__ void tc_commit2_pair(uint32_t own_addr) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(
+                     own_addr),
+                 "h"((uint16_t)3)
+                 : "memory");
+}
 __device__ __forceinline__ void tc_mma2_mxf4(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
                                              uint32_t sfa_tmem, uint32_t sfb_tmem, uint32_t accumulate) {
     asm volatile(
@@ -619,46 +627,52 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
             uint32_t s = 0, ph = 0, slot = 0, as = 0, aph = 0;
             const uint32_t idesc0 = make_idesc2(BN, 0), idesc1 = make_idesc2(BN, 2);
             const uint32_t a_base = smem_u32(s_a), b_base = smem_u32(s_b);
-            const uint32_t empty_own = smem_u32(&empty[0]), empty_peer = mapa_u32(smem_u32(&empty[0]), 1);
-            const uint32_t accf_own = smem_u32(&acc_full[0]), accf_peer = mapa_u32(smem_u32(&acc_full[0]), 1);
+            const uint32_t empty_own = smem_u32(&empty[0]), accf_own = smem_u32(&acc_full[0]);
             for (int tile = cluster_id; tile < n_tiles_total && !*dead; tile += n_clusters) {
                 if (!gemm_wait(&acc_empty[as], aph ^ 1, WAIT_GEMM_ACC_EMPTY, dead)) break;
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + as * BN;
-                for (int ks = 0; ks < k_stages; ++ks) {
+                // Two stages per trip when two are left: the fixed cost of a trip (barrier polls, fence,
+                // warp re-convergence) is then paid once per eight MMAs.
+                for (int ks = 0; ks < k_stages;) {
+                    const int n2 = (ks + 1 < k_stages) ? 2 : 1;
+                    const uint32_t s1 = (s + 1 == C::STAGES) ? 0 : s + 1, ph1 = (s + 1 == C::STAGES) ? ph ^ 1 : ph;
+                    const uint32_t slot1 = (slot + 1 == C::SF_SLOTS) ? 0 : slot + 1;
                     // the feeders arrive only after the stage's copies have landed in BOTH CTAs, so this
-                    // one barrier covers operands and scales
-                    TRACE(1, tile == cluster_id ? ks : 32 + ks);
+                    // one barrier per stage covers operands and scales
                     if (!gemm_wait(&sf_full[s], ph, WAIT_GEMM_SF, dead)) break;
-                    TRACE(2, tile == cluster_id ? ks : 32 + ks);
+                    if (n2 == 2 && !gemm_wait(&sf_full[s1], ph1, WAIT_GEMM_SF, dead)) break;
                     tc_fence_after();
-                    const int nch = min(2, p.k_chunks - 2 * ks);
-                    const uint32_t sf_tmem = tmem_base + C::SF_COL0 + slot * C::SF_COLS;
-                    const uint64_t adesc = make_desc_sw128(a_base + s * C::A_BYTES);
-                    const uint64_t bdesc = make_desc_sw128(b_base + s * C::B_BYTES);
-                    TRACE(11, tile == cluster_id ? ks : 32 + ks);
                     if (elect_one()) {
-                        tc_mma2_mxf4(d_tmem, adesc, bdesc, idesc0, sf_tmem, sf_tmem + 8, ks != 0);
-                        tc_mma2_mxf4(d_tmem, adesc + 2, bdesc + 2, idesc1, sf_tmem | (2u << 30), (sf_tmem + 8) | (2u << 30), 1);
-                        if (nch == 2) {
-                            tc_mma2_mxf4(d_tmem, adesc + 4, bdesc + 4, idesc0, sf_tmem + 4, sf_tmem + 8 + C::SFB_ST, 1);
-                            tc_mma2_mxf4(d_tmem, adesc + 6, bdesc + 6, idesc1, (sf_tmem + 4) | (2u << 30),
-                                         (sf_tmem + 8 + C::SFB_ST) | (2u << 30), 1);
+#pragma unroll
+                        for (int h = 0; h < 2; ++h) {
+                            if (h < n2) {
+                                const uint32_t sh = h ? s1 : s, sloth = h ? slot1 : slot;
+                                const int nch = min(2, p.k_chunks - 2 * (ks + h));
+                                const uint32_t sf_tmem = tmem_base + C::SF_COL0 + sloth * C::SF_COLS;
+                                const uint64_t adesc = make_desc_sw128(a_base + sh * C::A_BYTES);
+                                const uint64_t bdesc = make_desc_sw128(b_base + sh * C::B_BYTES);
+                                tc_mma2_mxf4(d_tmem, adesc, bdesc, idesc0, sf_tmem, sf_tmem + 8, (ks + h) != 0);
+                                tc_mma2_mxf4(d_tmem, adesc + 2, bdesc + 2, idesc1, sf_tmem | (2u << 30), (sf_tmem + 8) | (2u << 30), 1);
+                                if (nch == 2) {
+                                    tc_mma2_mxf4(d_tmem, adesc + 4, bdesc + 4, idesc0, sf_tmem + 4, sf_tmem + 8 + C::SFB_ST, 1);
+                                    tc_mma2_mxf4(d_tmem, adesc + 6, bdesc + 6, idesc1, (sf_tmem + 4) | (2u << 30),
+                                                 (sf_tmem + 8 + C::SFB_ST) | (2u << 30), 1);
+                                }
+                                // one completion event, signalled to both CTAs: frees the operand stage and the scale slot
+                                tc_commit2_pair(empty_own + sh * 8);
+                            }
                         }
-                        TRACE(12, tile == cluster_id ? ks : 32 + ks);
-                        // one completion event, signalled to both CTAs: frees the operand stage and the scale slot
-                        tc_commit2(empty_own + s * 8);
-                        tc_commit2(empty_peer + s * 8);
                     }
                     __syncwarp();
                     TRACE(3, tile == cluster_id ? ks : 32 + ks);
-                    if (++s == C::STAGES) s = 0, ph ^= 1;
-                    if (++slot == C::SF_SLOTS) slot = 0;
+                    for (int h = 0; h < n2; ++h) {
+                        if (++s == C::STAGES) s = 0, ph ^= 1;
+                        if (++slot == C::SF_SLOTS) slot = 0;
+                    }
+                    ks += n2;
                 }
-                if (elect_one()) {
-                    tc_commit2(accf_own + as * 8);
-                    tc_commit2(accf_peer + as * 8);
-                }
+                if (elect_one()) tc_commit2_pair(accf_own + as * 8);
                 __syncwarp();
                 if (++as == C::ACC_STAGES) as = 0, aph ^= 1;
             }
