@@ -41,6 +41,7 @@ __device__ long long g_trace[16][64];
 constexpr int BM = 128;
 constexpr int BK_BYTES = 128;   // 256 e2m1 elements per stage along K
 constexpr int GEMM_THREADS = 320;  // warp 0 TMA, warp 1 MMA, warps 2-5 epilogue, warps 6-9 scale feeders
+constexpr int GEMM2_THREADS = 352; // two-CTA kernel: one more warp (10) that issues the scale copies
 
 template <int BN>
 struct GemmCfg {
@@ -535,7 +536,7 @@ __device__ __forceinline__ uint32_t make_idesc2(int n, uint32_t sf_id) {
 }
 
 template <int BN>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM2_THREADS, 1)
     gemm_mxfp4_2cta_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                            const __grid_constant__ CUtensorMap tm_d, const GemmParams p) {
     using C = Gemm2Cfg<BN>;
@@ -561,7 +562,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < C::STAGES; ++i) {
-            mbar_init(&full[i], 1);
+            mbar_init(&full[i], 2);  // operand producer + scale producer
             mbar_init(&empty[i], 1);
             mbar_init(&sf_full[i], 8);
         }
@@ -592,31 +593,37 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
     const int k_stages = (p.k_chunks + 1) >> 1;
     const int64_t sf_blocks_per_rowblock = p.k_chunks;
 
-    if (warp == 0) {
-        // ------------------------------ TMA producer (both CTAs) ------------------------------
+    if (warp == 0 || warp == 10) {
+        // ------------------------------ TMA producers (both CTAs) ------------------------------
+        // warp 0 issues the two operand tensor copies of a stage, warp 10 the stage's scale blocks;
+        // both count on the stage's one `full` barrier.  (One thread issuing all five copies of a stage
+        // could not keep up with the tensor pipe.)
         if (lane == 0) {
-            uint32_t it = 0;
+            const bool ops_role = warp == 0;
+            uint32_t s = 0, ph = 0;
             for (int tile = cluster_id; tile < n_tiles_total && !*dead; tile += n_clusters) {
                 const int m_blk = (tile % m_pairs) * 2 + (int)rank, n_blk = tile / m_pairs;
                 const int m0 = m_blk * BM, n0 = n_blk * BN;
                 const int blk0 = n0 / 128;
                 const int n_blocks = (min(n0 + BN, p.N) - 1) / 128 - blk0 + 1;
-                for (int ks = 0; ks < k_stages; ++ks, ++it) {
-                    const int s = it % C::STAGES;
-                    const uint32_t ph = (it / C::STAGES) & 1;
+                const uint8_t* sfa_src = p.a_sf + (int64_t)m_blk * sf_blocks_per_rowblock * 512;
+                const uint8_t* sfb_src = p.b_sf + (int64_t)blk0 * sf_blocks_per_rowblock * 512;
+                for (int ks = 0; ks < k_stages; ++ks) {
                     if (!gemm_wait(&empty[s], ph ^ 1, WAIT_GEMM_EMPTY, dead)) break;
-                    TRACE(0, it);
-                    TRACE_PEER(6, it);
-                    const int nch = min(2, p.k_chunks - 2 * ks);
-                    mbar_arrive_expect_tx(&full[s], C::A_BYTES + C::B_BYTES + nch * 512 * (1 + n_blocks));
-                    tma_load_2d(s_a + s * C::A_BYTES, &tm_a, ks * BK_BYTES, m0, &full[s]);
-                    tma_load_2d(s_b + s * C::B_BYTES, &tm_b, ks * BK_BYTES, n0 + (int)rank * (BN / 2), &full[s]);
-                    bulk_load(s_sfa + s * C::SFA_BYTES, p.a_sf + ((int64_t)m_blk * sf_blocks_per_rowblock + 2 * ks) * 512,
-                              nch * 512, &full[s]);
-                    for (int rb = 0; rb < n_blocks; ++rb)
-                        bulk_load(s_sfb + s * C::SFB_BYTES + rb * 1024,
-                                  p.b_sf + ((int64_t)(blk0 + rb) * sf_blocks_per_rowblock + 2 * ks) * 512, nch * 512,
-                                  &full[s]);
+                    if (ops_role) {
+                        TRACE(0, tile == cluster_id ? ks : 32 + ks);
+                        mbar_arrive_expect_tx(&full[s], C::A_BYTES + C::B_BYTES);
+                        tma_load_2d(s_a + s * C::A_BYTES, &tm_a, ks * BK_BYTES, m0, &full[s]);
+                        tma_load_2d(s_b + s * C::B_BYTES, &tm_b, ks * BK_BYTES, n0 + (int)rank * (BN / 2), &full[s]);
+                    } else {
+                        const int nch = min(2, p.k_chunks - 2 * ks);
+                        mbar_arrive_expect_tx(&full[s], nch * 512 * (1 + n_blocks));
+                        bulk_load(s_sfa + s * C::SFA_BYTES, sfa_src + (int64_t)ks * 1024, nch * 512, &full[s]);
+                        for (int rb = 0; rb < n_blocks; ++rb)
+                            bulk_load(s_sfb + s * C::SFB_BYTES + rb * 1024,
+                                      sfb_src + ((int64_t)rb * sf_blocks_per_rowblock + 2 * ks) * 512, nch * 512, &full[s]);
+                    }
+                    if (++s == C::STAGES) s = 0, ph ^= 1;
                 }
             }
         }
@@ -677,7 +684,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
                 if (++as == C::ACC_STAGES) as = 0, aph ^= 1;
             }
         }
-    } else if (warp >= 6) {
+    } else if (warp >= 6 && warp <= 9) {
         // ------------------------------ scale feeders (both CTAs) ------------------------------
         const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
         uint32_t it = 0;
@@ -731,7 +738,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
                 if (warp == 6 && lane == 0) { TRACE(5, it); TRACE_PEER(8, it); }
             }
         }
-    } else {
+    } else if (warp >= 2 && warp <= 5) {
         // ------------------------------ epilogue (both CTAs) ------------------------------
         const int q = warp & 3;
         uint8_t* stg = s_stg + (warp - 2) * 4096;
@@ -801,7 +808,7 @@ static int launch_gemm_2cta(const uint8_t* a, const uint8_t* b, void* d, const G
     if (cached_dev != dev) {
         cudaLaunchConfig_t cfg = {};
         cfg.gridDim = dim3((unsigned)sms, 1, 1);
-        cfg.blockDim = dim3(GEMM_THREADS, 1, 1);
+        cfg.blockDim = dim3(GEMM2_THREADS, 1, 1);
         cfg.dynamicSmemBytes = C::SMEM;
         cudaLaunchAttribute attr;
         attr.id = cudaLaunchAttributeClusterDimension;
@@ -815,7 +822,7 @@ static int launch_gemm_2cta(const uint8_t* a, const uint8_t* b, void* d, const G
     }
     const int pair_tiles = (p.m_tiles / 2) * p.n_tiles;
     const int clusters = pair_tiles < cached_clusters ? pair_tiles : cached_clusters;
-    kern<<<clusters * 2, GEMM_THREADS, C::SMEM, stream>>>(tm_a, tm_b, tm_d, p);
+    kern<<<clusters * 2, GEMM2_THREADS, C::SMEM, stream>>>(tm_a, tm_b, tm_d, p);
 #ifdef QUARTET_GEMM_TRACE
     {
         static long long h[16][64];
