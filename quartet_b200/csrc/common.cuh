@@ -56,6 +56,7 @@ enum : int32_t {
     WAIT_GEMM_ACC_FULL = 4,
     WAIT_GEMM_ACC_EMPTY = 5,
     WAIT_GEMM_SF = 6,
+    WAIT_GEMM_ALIGN = 7,  // not a wait: dynamic shared memory was not 1024-byte aligned
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }

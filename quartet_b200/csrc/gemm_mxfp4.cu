@@ -41,7 +41,7 @@ __device__ long long g_trace[16][64];
 constexpr int BM = 128;
 constexpr int BK_BYTES = 128;   // 256 e2m1 elements per stage along K
 constexpr int GEMM_THREADS = 320;  // warp 0 TMA, warp 1 MMA, warps 2-5 epilogue, warps 6-9 scale feeders
-constexpr int GEMM2_THREADS = 352; // two-CTA kernel: one more warp (10) that issues the scale copies
+constexpr int GEMM2_THREADS = 480; // two-CTA kernel: warp 10 issues the scale copies, warps 11-14 are four more epilogue warps
 
 template <int BN>
 struct GemmCfg {
@@ -177,6 +177,7 @@ __device__ __forceinline__ bool gemm_wait(uint64_t* bar, uint32_t parity, int32_
 // mask + un-rotation (the 32 columns are exactly one Hadamard group), convert, stage 32 rows x 64
 // bytes in 64B-swizzled shared memory and hand them to TMA -- one store for bf16, two (16 columns
 // each) for fp32.  Two 2 KB staging buffers per warp alternate.
+template <int NBUF>
 __device__ __forceinline__ void epilogue_block(const uint32_t (&r)[32], const GemmParams& p, const CUtensorMap* tm_d,
                                                int64_t row, int row0, int col, uint8_t* stg, uint32_t& n_stores, int lane) {
     float v[32];
@@ -193,8 +194,8 @@ __device__ __forceinline__ void epilogue_block(const uint32_t (&r)[32], const Ge
     if (p.d_f32) {
 #pragma unroll
         for (int hf = 0; hf < 2; ++hf, ++n_stores) {
-            uint8_t* buf = stg + (n_stores & 1) * 2048;
-            if (lane == 0) bulk_wait_read1();
+            uint8_t* buf = stg + (NBUF == 2 ? (n_stores & 1) * 2048 : 0);
+            if (lane == 0) { if (NBUF == 2) bulk_wait_read1(); else bulk_wait_read0(); }
             __syncwarp();
             uint8_t* dst = buf + lane * 64;
 #pragma unroll
@@ -209,9 +210,9 @@ __device__ __forceinline__ void epilogue_block(const uint32_t (&r)[32], const Ge
             }
         }
     } else {
-        uint8_t* buf = stg + (n_stores & 1) * 2048;
+        uint8_t* buf = stg + (NBUF == 2 ? (n_stores & 1) * 2048 : 0);
         ++n_stores;
-        if (lane == 0) bulk_wait_read1();
+        if (lane == 0) { if (NBUF == 2) bulk_wait_read1(); else bulk_wait_read0(); }
         __syncwarp();
         uint8_t* dst = buf + lane * 64;
 #pragma unroll
@@ -405,7 +406,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_mxfp4_kernel(const __gri
                 uint32_t r[32];
                 tc_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + C::ACC_COL0 + as * BN + ch * 32, r);
                 tc_wait_ld();
-                epilogue_block(r, p, &tm_d, row, row0, n0 + ch * 32, stg, n_stores, lane);
+                epilogue_block<2>(r, p, &tm_d, row, row0, n0 + ch * 32, stg, n_stores, lane);
             }
             tc_fence_before();
             __syncwarp();
@@ -453,9 +454,9 @@ struct Gemm2Cfg {
     static constexpr int SFB_BLOCKS = (BN % 128 == 0) ? BN / 128 : BN / 128 + 2;  // 128-row scale blocks a tile can touch
     static constexpr int SFB_BYTES = SFB_BLOCKS * 1024;
     static constexpr int STAGE_BYTES = A_BYTES + B_BYTES + SFA_BYTES + SFB_BYTES;
-    static constexpr int STG_BYTES = 4 * 4096;               // epilogue staging: 2 x 2 KB per epilogue warp
-    static constexpr int STAGES = (232448 - STG_BYTES - 512 - 1024) / STAGE_BYTES;
-    static constexpr int SMEM = STAGES * STAGE_BYTES + STG_BYTES + 512 + 1024;
+    static constexpr int STG_BYTES = 8 * 2048;               // epilogue staging: 2 KB per epilogue warp (8 warps)
+    static constexpr int STAGES = (232448 - STG_BYTES - 256) / STAGE_BYTES;
+    static constexpr int SMEM = STAGES * STAGE_BYTES + STG_BYTES + 256;
     static_assert(SF_COL0 + SF_SLOTS * SF_COLS <= TMEM_COLS, "tensor memory budget");
     static_assert(SF_SLOTS < STAGES, "scale slots are recycled through the stage barriers");
     static_assert(B_BYTES % 1024 == 0, "operand stages stay 1024-byte aligned");
@@ -540,8 +541,14 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM2_THREADS, 1)
     gemm_mxfp4_2cta_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                            const __grid_constant__ CUtensorMap tm_d, const GemmParams p) {
     using C = Gemm2Cfg<BN>;
-    extern __shared__ uint8_t smem_raw[];
-    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    // Dynamic shared memory is the kernel's only shared memory and starts 1024-byte aligned (checked
+    // below); no slack is reserved for re-aligning it, which is what makes room for a sixth stage.
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    uint8_t* smem = smem_raw;
+    if (smem_u32(smem) & 1023u) {
+        if (threadIdx.x == 0) atomicOr(&g_status, WAIT_GEMM_ALIGN | 0x100);
+        return;
+    }
     uint8_t* s_a = smem;
     uint8_t* s_b = s_a + C::STAGES * C::A_BYTES;
     uint8_t* s_stg = s_b + C::STAGES * C::B_BYTES;
@@ -568,7 +575,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM2_THREADS, 1)
         }
         for (int i = 0; i < C::ACC_STAGES; ++i) {
             mbar_init(&acc_full[i], 1);
-            mbar_init(&acc_empty[i], 8);
+            mbar_init(&acc_empty[i], 16);  // 8 epilogue warps in each CTA
         }
         *dead = 0;
         fence_mbar_init();
@@ -609,6 +616,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM2_THREADS, 1)
                 const uint8_t* sfa_src = p.a_sf + (int64_t)m_blk * sf_blocks_per_rowblock * 512;
                 const uint8_t* sfb_src = p.b_sf + (int64_t)blk0 * sf_blocks_per_rowblock * 512;
                 for (int ks = 0; ks < k_stages; ++ks) {
+                    if (ops_role) TRACE(13, tile == cluster_id ? ks : 32 + ks);
                     if (!gemm_wait(&empty[s], ph ^ 1, WAIT_GEMM_EMPTY, dead)) break;
                     if (ops_role) {
                         TRACE(0, tile == cluster_id ? ks : 32 + ks);
@@ -639,16 +647,18 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM2_THREADS, 1)
                 if (!gemm_wait(&acc_empty[as], aph ^ 1, WAIT_GEMM_ACC_EMPTY, dead)) break;
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + as * BN;
-                // Two stages per trip when two are left: the fixed cost of a trip (barrier polls, fence,
-                // warp re-convergence) is then paid once per eight MMAs.
+                // Two stages per trip when the second is ready as well: the fixed cost of a trip (barrier
+                // polls, fence, warp re-convergence) is then paid once per eight MMAs.
                 for (int ks = 0; ks < k_stages;) {
-                    const int n2 = (ks + 1 < k_stages) ? 2 : 1;
+                    int n2 = (ks + 1 < k_stages) ? 2 : 1;
                     const uint32_t s1 = (s + 1 == C::STAGES) ? 0 : s + 1, ph1 = (s + 1 == C::STAGES) ? ph ^ 1 : ph;
                     const uint32_t slot1 = (slot + 1 == C::SF_SLOTS) ? 0 : slot + 1;
                     // the feeders arrive only after the stage's copies have landed in BOTH CTAs, so this
                     // one barrier per stage covers operands and scales
+                    TRACE(1, tile == cluster_id ? ks : 32 + ks);
                     if (!gemm_wait(&sf_full[s], ph, WAIT_GEMM_SF, dead)) break;
-                    if (n2 == 2 && !gemm_wait(&sf_full[s1], ph1, WAIT_GEMM_SF, dead)) break;
+                    if (n2 == 2 && !mbar_try_wait(&sf_full[s1], ph1)) n2 = 1;  // pair up only if the next stage is ready too
+                    TRACE(2, tile == cluster_id ? ks : 32 + ks);
                     tc_fence_after();
                     if (elect_one()) {
 #pragma unroll
@@ -738,10 +748,13 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM2_THREADS, 1)
                 if (warp == 6 && lane == 0) { TRACE(5, it); TRACE_PEER(8, it); }
             }
         }
-    } else if (warp >= 2 && warp <= 5) {
+    } else if ((warp >= 2 && warp <= 5) || warp >= 11) {
         // ------------------------------ epilogue (both CTAs) ------------------------------
+        // Two warps per TMEM lane quadrant: warps 2-5 drain the even 32-column blocks of the tile,
+        // warps 11-14 the odd ones; the next block's tcgen05.ld is in flight while one is processed.
         const int q = warp & 3;
-        uint8_t* stg = s_stg + (warp - 2) * 4096;
+        const int par = warp >= 11 ? 1 : 0;
+        uint8_t* stg = s_stg + (par * 4 + q) * 2048;
         uint32_t acc_it = 0, n_stores = 0;
         for (int tile = cluster_id; tile < n_tiles_total && !*dead; tile += n_clusters, ++acc_it) {
             const int m_blk = (tile % m_pairs) * 2 + (int)rank, n_blk = tile / m_pairs;
@@ -753,11 +766,18 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM2_THREADS, 1)
             const int row0 = m_blk * BM + q * 32;
             const int64_t row = (int64_t)row0 + lane;
             const int n_chunks = min(BN, p.N - n0) / 32;
-            for (int ch = 0; ch < n_chunks; ++ch) {
-                uint32_t r[32];
-                tc_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + as * BN + ch * 32, r);
+            const uint32_t t0 = tmem_base + ((uint32_t)(q * 32) << 16) + as * BN;
+            uint32_t ra[32], rb[32];
+            if (par < n_chunks) tc_ld32(t0 + par * 32, ra);
+            for (int ch = par; ch < n_chunks; ch += 4) {
                 tc_wait_ld();
-                epilogue_block(r, p, &tm_d, row, row0, n0 + ch * 32, stg, n_stores, lane);
+                if (ch + 2 < n_chunks) tc_ld32(t0 + (ch + 2) * 32, rb);
+                epilogue_block<1>(ra, p, &tm_d, row, row0, n0 + ch * 32, stg, n_stores, lane);
+                if (ch + 2 < n_chunks) {
+                    tc_wait_ld();
+                    if (ch + 4 < n_chunks) tc_ld32(t0 + (ch + 4) * 32, ra);
+                    epilogue_block<1>(rb, p, &tm_d, row, row0, n0 + (ch + 2) * 32, stg, n_stores, lane);
+                }
             }
             tc_fence_before();
             __syncwarp();
@@ -830,10 +850,10 @@ static int launch_gemm_2cta(const uint8_t* a, const uint8_t* b, void* d, const G
         if (cudaMemcpyFromSymbol(h, g_trace, sizeof(h)) == cudaSuccess) {
             const char* names[9] = {"prod:empty_ok", "mma:full_ok", "mma:sf_ok", "mma:commit", "feed:full_ok", "feed:arrive",
                                     "PEER prod:empty_ok", "PEER feed:full_ok", "PEER feed:arrive"};
-            for (int i = 0; i < 64; ++i)
-                fprintf(stderr, "it %2d loop_top=%6lld sf_ok=+%lld premma=+%lld mmas=+%lld commits=+%lld | prod_empty_ok=%6lld feed_full_ok=%6lld feed_arrive=%6lld\n", i,
-                        h[1][i] - h[0][0], h[2][i] - h[1][i], h[11][i] - h[2][i], h[12][i] - h[11][i], h[3][i] - h[12][i], h[0][i] - h[0][0],
-                        h[4][i] - h[0][0], h[5][i] - h[0][0]);
+            for (int i = 32; i < 64; ++i)
+                fprintf(stderr, "it %2d mma: top=%6lld wait=+%lld issue=+%lld | prod: top=%6lld wait=+%lld | feed: full_ok=%6lld arrive=+%lld\n", i,
+                        h[1][i] - h[13][32], h[2][i] - h[1][i], h[3][i] - h[2][i], h[13][i] - h[13][32], h[0][i] - h[13][i],
+                        h[4][i] - h[13][32], h[5][i] - h[4][i]);
             for (int i = 0; i < 4; ++i) fprintf(stderr, "tile %d epi:acc_full_ok=%lld epi:done=%lld\n", i, h[9][i] - h[0][0], h[10][i] - h[0][0]);
         }
     }
