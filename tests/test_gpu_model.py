@@ -1,0 +1,65 @@
+"""Model-level use of the drop-in package: a small Llama-style decoder whose block linears are
+QuantizedLinear (production quantizer / scheme names), bf16 autocast around forward AND backward as
+the reference's training loop does (src/optim/base.py:190-200)."""
+import copy
+
+import pytest
+import torch
+
+from tests.llama_harness import TinyLlama
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def Q():
+    import __graft_entry__ as entry
+
+    entry.build()
+    import quartet_b200.quantization as q
+
+    return q
+
+
+def _step(model, idx, tgt):
+    for p in model.parameters():
+        p.grad = None
+    with torch.autocast("cuda", dtype=torch.bfloat16):
+        loss = model(idx, tgt)
+        loss.backward()
+    return loss
+
+
+def test_fused_path_matches_composed_modules_at_model_level(Q, monkeypatch):
+    torch.manual_seed(0)
+    gkw = {"stochastic": False, "rerotate": "signs"}  # deterministic rounding so both paths are comparable
+    fused = TinyLlama(Q, gkw=gkw).cuda()
+    composed = copy.deepcopy(fused)
+    idx = torch.randint(0, 512, (4, 128), device="cuda")
+    tgt = torch.randint(0, 512, (4, 128), device="cuda")
+    l1 = _step(fused, idx, tgt)
+    monkeypatch.setattr(Q.QuantizedLinear, "_fusable", lambda self, x: False)  # compose quantizer modules + F.linear
+    l2 = _step(composed, idx, tgt)
+    assert abs(l1.item() - l2.item()) < 2e-2 * abs(l2.item())
+    for (n1, p1), (_, p2) in zip(fused.named_parameters(), composed.named_parameters()):
+        assert p1.grad is not None and torch.isfinite(p1.grad).all(), n1
+        cos = torch.nn.functional.cosine_similarity(p1.grad.flatten().float(), p2.grad.flatten().float(), dim=0).item()
+        assert cos > 0.98, (n1, cos)
+
+
+def test_training_reduces_loss(Q):
+    from quartet_b200 import ops
+
+    torch.manual_seed(1)
+    model = TinyLlama(Q).cuda()
+    opt = torch.optim.AdamW(model.parameters(), lr=3e-3)
+    idx = torch.randint(0, 512, (8, 128), device="cuda")
+    tgt = torch.roll(idx, -1, 1)
+    losses = []
+    for _ in range(30):
+        losses.append(_step(model, idx, tgt).item())
+        opt.step()
+    print("loss", losses[0], "->", losses[-1])
+    assert losses[-1] < 0.7 * losses[0]
+    assert list(model.blocks[0].c_attn.state_dict().keys()) == ["weight"]
+    assert ops.device_status() == 0
