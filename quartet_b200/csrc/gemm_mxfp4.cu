@@ -445,8 +445,14 @@ struct Gemm2Cfg {
     static constexpr int SFB_ST = NSEG <= 4 ? 4 : 8;         // columns written per tcgen05.st
     static constexpr int SF_COLS = 8 + 2 * SFB_ST;           // SFA 2 x 4, SFB 2 x SFB_ST columns per stage
     static constexpr int ACC_STAGES = (2 * BN + 2 * SF_COLS <= 512) ? 2 : 1;
-    static constexpr int SF_SLOTS = (512 - ACC_STAGES * BN) / SF_COLS >= 4 ? 4 : 2;
-    static constexpr int SF_COL0 = ACC_STAGES * BN;
+    // A 256-column accumulator leaves no room for a second one beside the scales.  Consecutive tiles
+    // then alternate between columns [0, 256) and [128, 384): the two share only columns [128, 256),
+    // which the epilogue pulls into registers first, so the next tile's MMAs start after a quarter of
+    // a drain instead of a whole epilogue.
+    static constexpr bool OVERLAP = ACC_STAGES == 1;
+    static constexpr int ACC_SHIFT = 128;
+    static constexpr int SF_COL0 = OVERLAP ? BN + ACC_SHIFT : ACC_STAGES * BN;
+    static constexpr int SF_SLOTS = (512 - SF_COL0) / SF_COLS >= 4 ? 4 : 2;
     static constexpr int TMEM_COLS = 512;
     static constexpr int A_BYTES = BM * BK_BYTES;            // 16 KB
     static constexpr int B_BYTES = (BN / 2) * BK_BYTES;      // this CTA's half of the B tile
@@ -536,6 +542,18 @@ __device__ __forceinline__ uint32_t make_idesc2(int n, uint32_t sf_id) {
     return d;
 }
 
+// Tile order of the persistent two-CTA kernel.  Tiles that run at the same time (consecutive
+// indices) form a compact block of RASTER_BAND row pairs by as many column tiles, so that the rows of A
+// and B a wave reads are few and each is shared by many CTAs while it is hot in the L2 of their die.
+constexpr int RASTER_BAND = 8;
+__device__ __forceinline__ void tile_coords(int tile, int m_pairs, int n_tiles, int& m_pair, int& n_blk) {
+    const int per_band = RASTER_BAND * n_tiles;
+    const int band = tile / per_band, within = tile - band * per_band;
+    const int rows = min(RASTER_BAND, m_pairs - band * RASTER_BAND);
+    n_blk = within / rows;
+    m_pair = band * RASTER_BAND + (within - n_blk * rows);
+}
+
 template <int BN>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM2_THREADS, 1)
     gemm_mxfp4_2cta_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
@@ -608,18 +626,22 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM2_THREADS, 1)
         if (lane == 0) {
             const bool ops_role = warp == 0;
             uint32_t s = 0, ph = 0;
+            [[maybe_unused]] uint32_t tr = 0;
             for (int tile = cluster_id; tile < n_tiles_total && !*dead; tile += n_clusters) {
-                const int m_blk = (tile % m_pairs) * 2 + (int)rank, n_blk = tile / m_pairs;
+                int m_pair, n_blk;
+                tile_coords(tile, m_pairs, p.n_tiles, m_pair, n_blk);
+                const int m_blk = m_pair * 2 + (int)rank;
                 const int m0 = m_blk * BM, n0 = n_blk * BN;
                 const int blk0 = n0 / 128;
                 const int n_blocks = (min(n0 + BN, p.N) - 1) / 128 - blk0 + 1;
                 const uint8_t* sfa_src = p.a_sf + (int64_t)m_blk * sf_blocks_per_rowblock * 512;
                 const uint8_t* sfb_src = p.b_sf + (int64_t)blk0 * sf_blocks_per_rowblock * 512;
                 for (int ks = 0; ks < k_stages; ++ks) {
-                    if (ops_role) TRACE(13, tile == cluster_id ? ks : 32 + ks);
+                    if (ops_role) TRACE(13, tr);
                     if (!gemm_wait(&empty[s], ph ^ 1, WAIT_GEMM_EMPTY, dead)) break;
                     if (ops_role) {
-                        TRACE(0, tile == cluster_id ? ks : 32 + ks);
+                        TRACE(0, tr);
+                        ++tr;
                         mbar_arrive_expect_tx(&full[s], C::A_BYTES + C::B_BYTES);
                         tma_load_2d(s_a + s * C::A_BYTES, &tm_a, ks * BK_BYTES, m0, &full[s]);
                         tma_load_2d(s_b + s * C::B_BYTES, &tm_b, ks * BK_BYTES, n0 + (int)rank * (BN / 2), &full[s]);
@@ -639,14 +661,16 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM2_THREADS, 1)
         // ------------------------------ MMA issuer (leader CTA only) ------------------------------
         if (leader) {
             // ring positions are kept as (index, phase) pairs: no division in the issue loop
-            uint32_t s = 0, ph = 0, slot = 0, as = 0, aph = 0;
+            uint32_t s = 0, ph = 0, slot = 0, as = 0, aph = 0, acc_it = 0;
+            [[maybe_unused]] uint32_t tr = 0;
             const uint32_t idesc0 = make_idesc2(BN, 0), idesc1 = make_idesc2(BN, 2);
             const uint32_t a_base = smem_u32(s_a), b_base = smem_u32(s_b);
             const uint32_t empty_own = smem_u32(&empty[0]), accf_own = smem_u32(&acc_full[0]);
             for (int tile = cluster_id; tile < n_tiles_total && !*dead; tile += n_clusters) {
                 if (!gemm_wait(&acc_empty[as], aph ^ 1, WAIT_GEMM_ACC_EMPTY, dead)) break;
                 tc_fence_after();
-                const uint32_t d_tmem = tmem_base + as * BN;
+                const uint32_t d_tmem = tmem_base + (C::OVERLAP ? (acc_it & 1) * C::ACC_SHIFT : as * BN);
+                ++acc_it;
                 // Two stages per trip when the second is ready as well: the fixed cost of a trip (barrier
                 // polls, fence, warp re-convergence) is then paid once per eight MMAs.
                 for (int ks = 0; ks < k_stages;) {
@@ -655,10 +679,10 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM2_THREADS, 1)
                     const uint32_t slot1 = (slot + 1 == C::SF_SLOTS) ? 0 : slot + 1;
                     // the feeders arrive only after the stage's copies have landed in BOTH CTAs, so this
                     // one barrier per stage covers operands and scales
-                    TRACE(1, tile == cluster_id ? ks : 32 + ks);
+                    TRACE(1, tr);
                     if (!gemm_wait(&sf_full[s], ph, WAIT_GEMM_SF, dead)) break;
                     if (n2 == 2 && !mbar_try_wait(&sf_full[s1], ph1)) n2 = 1;  // pair up only if the next stage is ready too
-                    TRACE(2, tile == cluster_id ? ks : 32 + ks);
+                    TRACE(2, tr);
                     tc_fence_after();
                     if (elect_one()) {
 #pragma unroll
@@ -682,7 +706,9 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM2_THREADS, 1)
                         }
                     }
                     __syncwarp();
-                    TRACE(3, tile == cluster_id ? ks : 32 + ks);
+                    TRACE(3, tr);
+                    if (n2 == 2) TRACE(11, tr + 1);
+                    tr += n2;
                     for (int h = 0; h < n2; ++h) {
                         if (++s == C::STAGES) s = 0, ph ^= 1;
                         if (++slot == C::SF_SLOTS) slot = 0;
@@ -699,7 +725,9 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM2_THREADS, 1)
         const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
         uint32_t it = 0;
         for (int tile = cluster_id; tile < n_tiles_total && !*dead; tile += n_clusters) {
-            const int n0 = (tile / m_pairs) * BN;
+            int m_pair, n_blk;
+            tile_coords(tile, m_pairs, p.n_tiles, m_pair, n_blk);
+            const int n0 = n_blk * BN;
             const int seg0 = (n0 % 128) / 32;
             for (int ks = 0; ks < k_stages; ++ks, ++it) {
                 const int s = it % C::STAGES;
@@ -757,7 +785,9 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM2_THREADS, 1)
         uint8_t* stg = s_stg + (par * 4 + q) * 2048;
         uint32_t acc_it = 0, n_stores = 0;
         for (int tile = cluster_id; tile < n_tiles_total && !*dead; tile += n_clusters, ++acc_it) {
-            const int m_blk = (tile % m_pairs) * 2 + (int)rank, n_blk = tile / m_pairs;
+            int m_pair, n_blk;
+            tile_coords(tile, m_pairs, p.n_tiles, m_pair, n_blk);
+            const int m_blk = m_pair * 2 + (int)rank;
             const int n0 = n_blk * BN;
             const int as = acc_it % C::ACC_STAGES;
             if (!gemm_wait(&acc_full[as], (acc_it / C::ACC_STAGES) & 1, WAIT_GEMM_ACC_FULL, dead)) break;
@@ -766,22 +796,44 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM2_THREADS, 1)
             const int row0 = m_blk * BM + q * 32;
             const int64_t row = (int64_t)row0 + lane;
             const int n_chunks = min(BN, p.N - n0) / 32;
-            const uint32_t t0 = tmem_base + ((uint32_t)(q * 32) << 16) + as * BN;
             uint32_t ra[32], rb[32];
-            if (par < n_chunks) tc_ld32(t0 + par * 32, ra);
-            for (int ch = par; ch < n_chunks; ch += 4) {
+            if constexpr (C::OVERLAP) {
+                // this warp's four blocks, those in the shared columns first
+                const uint32_t t0 = tmem_base + ((uint32_t)(q * 32) << 16) + (acc_it & 1) * C::ACC_SHIFT;
+                const int shared0 = (acc_it & 1) ? 0 : C::ACC_SHIFT / 32;
+                const int c0 = shared0 + par, c1 = c0 + 2, c2 = (shared0 ^ (C::ACC_SHIFT / 32)) + par, c3 = c2 + 2;
+                if (c0 < n_chunks) tc_ld32(t0 + c0 * 32, ra);
+                if (c1 < n_chunks) tc_ld32(t0 + c1 * 32, rb);
                 tc_wait_ld();
-                if (ch + 2 < n_chunks) tc_ld32(t0 + (ch + 2) * 32, rb);
-                epilogue_block<1>(ra, p, &tm_d, row, row0, n0 + ch * 32, stg, n_stores, lane);
-                if (ch + 2 < n_chunks) {
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive_cluster(mapa_u32(smem_u32(&acc_empty[0]), 0));
+                if (c0 < n_chunks) epilogue_block<1>(ra, p, &tm_d, row, row0, n0 + c0 * 32, stg, n_stores, lane);
+                if (c2 < n_chunks) tc_ld32(t0 + c2 * 32, ra);
+                if (c1 < n_chunks) epilogue_block<1>(rb, p, &tm_d, row, row0, n0 + c1 * 32, stg, n_stores, lane);
+                if (c3 < n_chunks) tc_ld32(t0 + c3 * 32, rb);
+                tc_wait_ld();
+                if (c2 < n_chunks) epilogue_block<1>(ra, p, &tm_d, row, row0, n0 + c2 * 32, stg, n_stores, lane);
+                if (c3 < n_chunks) epilogue_block<1>(rb, p, &tm_d, row, row0, n0 + c3 * 32, stg, n_stores, lane);
+                // all of this tile's tensor-memory reads are complete before the warp's next arrive
+                tc_fence_before();
+            } else {
+                const uint32_t t0 = tmem_base + ((uint32_t)(q * 32) << 16) + as * BN;
+                if (par < n_chunks) tc_ld32(t0 + par * 32, ra);
+                for (int ch = par; ch < n_chunks; ch += 4) {
                     tc_wait_ld();
-                    if (ch + 4 < n_chunks) tc_ld32(t0 + (ch + 4) * 32, ra);
-                    epilogue_block<1>(rb, p, &tm_d, row, row0, n0 + (ch + 2) * 32, stg, n_stores, lane);
+                    if (ch + 2 < n_chunks) tc_ld32(t0 + (ch + 2) * 32, rb);
+                    epilogue_block<1>(ra, p, &tm_d, row, row0, n0 + ch * 32, stg, n_stores, lane);
+                    if (ch + 2 < n_chunks) {
+                        tc_wait_ld();
+                        if (ch + 4 < n_chunks) tc_ld32(t0 + (ch + 4) * 32, ra);
+                        epilogue_block<1>(rb, p, &tm_d, row, row0, n0 + (ch + 2) * 32, stg, n_stores, lane);
+                    }
                 }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive_cluster(mapa_u32(smem_u32(&acc_empty[as]), 0));
             }
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive_cluster(mapa_u32(smem_u32(&acc_empty[as]), 0));
             if (warp == 2 && lane == 0) TRACE(10, acc_it);
         }
         if (lane == 0) bulk_wait0();
@@ -841,7 +893,10 @@ static int launch_gemm_2cta(const uint8_t* a, const uint8_t* b, void* d, const G
         if (getenv("QUARTET_GEMM_VERBOSE")) fprintf(stderr, "quartet: %d SMs, %d resident CTA pairs\n", sms, n);
     }
     const int pair_tiles = (p.m_tiles / 2) * p.n_tiles;
-    const int clusters = pair_tiles < cached_clusters ? pair_tiles : cached_clusters;
+    int clusters = pair_tiles < cached_clusters ? pair_tiles : cached_clusters;
+#ifdef QUARTET_GEMM_TRACE
+    if (const char* e = getenv("QUARTET_GEMM_MAX_CLUSTERS")) clusters = clusters < atoi(e) ? clusters : atoi(e);
+#endif
     kern<<<clusters * 2, GEMM2_THREADS, C::SMEM, stream>>>(tm_a, tm_b, tm_d, p);
 #ifdef QUARTET_GEMM_TRACE
     {
@@ -850,10 +905,15 @@ static int launch_gemm_2cta(const uint8_t* a, const uint8_t* b, void* d, const G
         if (cudaMemcpyFromSymbol(h, g_trace, sizeof(h)) == cudaSuccess) {
             const char* names[9] = {"prod:empty_ok", "mma:full_ok", "mma:sf_ok", "mma:commit", "feed:full_ok", "feed:arrive",
                                     "PEER prod:empty_ok", "PEER feed:full_ok", "PEER feed:arrive"};
-            for (int i = 32; i < 64; ++i)
-                fprintf(stderr, "it %2d mma: top=%6lld wait=+%lld issue=+%lld | prod: top=%6lld wait=+%lld | feed: full_ok=%6lld arrive=+%lld\n", i,
-                        h[1][i] - h[13][32], h[2][i] - h[1][i], h[3][i] - h[2][i], h[13][i] - h[13][32], h[0][i] - h[13][i],
-                        h[4][i] - h[13][32], h[5][i] - h[4][i]);
+            // per stage: producer issue time, then deltas: landed (feeder saw full), fed (feeder arrive), MMA saw
+            // sf_full, committed; `paired` marks the second stage of a two-stage trip; reuse = producer issue of it+STAGES
+            for (int i = 0; i < 40; ++i) {
+                const bool second = h[11][i] != 0 && h[1][i] == 0;
+                const long long issue = h[0][i], commit = second ? h[11][i] : h[3][i];
+                fprintf(stderr, "it %2d issue=%7lld land=+%5lld fed=+%4lld | mma %s commit=+%5lld (from fed) | reissue=+%5lld (from commit)\n", i,
+                        issue - h[0][0], h[4][i] - issue, h[5][i] - h[4][i], second ? "2nd" : "1st", commit - h[5][i],
+                        i + C::STAGES < 64 ? h[0][i + C::STAGES] - commit : 0);
+            }
             for (int i = 0; i < 4; ++i) fprintf(stderr, "tile %d epi:acc_full_ok=%lld epi:done=%lld\n", i, h[9][i] - h[0][0], h[10][i] - h[0][0]);
         }
     }
