@@ -9,19 +9,68 @@
 
 namespace quartet {
 
-// Unnormalised Sylvester-ordered WHT: w_j = sum_i x_i (-1)^popc(i & j).
+// Packed single-precision pairs (add/sub/mul/fma.f32x2): one issue slot for two IEEE fp32 operations,
+// each lane rounded exactly like its scalar counterpart.  The quantizers are bound by instruction
+// issue, not by memory, so halving the issue count of the butterflies is what matters.
+typedef unsigned long long f32x2_t;
+__device__ __forceinline__ f32x2_t pack2(float lo, float hi) {
+    f32x2_t r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ void unpack2(f32x2_t v, float& lo, float& hi) {
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ f32x2_t add2(f32x2_t a, f32x2_t b) {
+    f32x2_t r;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+__device__ __forceinline__ f32x2_t sub2(f32x2_t a, f32x2_t b) {
+    f32x2_t r;
+    asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+__device__ __forceinline__ f32x2_t mul2(f32x2_t a, f32x2_t b) {
+    f32x2_t r;
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+__device__ __forceinline__ f32x2_t fma2(f32x2_t a, f32x2_t b, f32x2_t c) {
+    f32x2_t r;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+    return r;
+}
+__device__ __forceinline__ float max3_abs(float m, float a, float b) {
+    float r;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(m), "f"(fabsf(a)), "f"(fabsf(b)));
+    return r;
+}
+
+// Unnormalised Sylvester-ordered WHT: w_j = sum_i x_i (-1)^popc(i & j).  The stride-1 butterflies run
+// as scalar operations while the pairs (2i, 2i+1) are formed; the four wider strides are packed.
+// Butterfly stages commute and every lane operation is the scalar one, so the result is bit-identical
+// to the plain five-stage network.
 __device__ __forceinline__ void wht32(float (&v)[32]) {
+    f32x2_t p[16];
 #pragma unroll
-    for (int s = 1; s < 32; s <<= 1) {
+    for (int i = 0; i < 16; ++i) {
+        const float a = v[2 * i], b = v[2 * i + 1];
+        p[i] = pack2(a + b, a - b);
+    }
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
+    for (int s = 1; s < 16; s <<= 1) {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
             if ((i & s) == 0) {
-                float a = v[i], b = v[i + s];
-                v[i] = a + b;
-                v[i + s] = a - b;
+                const f32x2_t a = p[i], b = p[i + s];
+                p[i] = add2(a, b);
+                p[i + s] = sub2(a, b);
             }
         }
     }
+#pragma unroll
+    for (int i = 0; i < 16; ++i) unpack2(p[i], v[2 * i], v[2 * i + 1]);
 }
 
 __device__ __forceinline__ void unpack_bf16x8(const uint4& q, float* out) {

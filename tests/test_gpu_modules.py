@@ -156,3 +156,25 @@ def test_ragged_token_count(Q):
     assert x.grad.shape == x.shape and torch.isfinite(x.grad.float()).all() and torch.isfinite(lin.weight.grad).all()
     ref = torch.nn.functional.linear(x.float(), lin.weight.float())
     assert ((y.float() - ref).norm() / ref.norm()).item() < 0.35
+
+
+def test_host_stager_orders_copies_against_compute():
+    from quartet_b200.staging import HostStager
+
+    dev = torch.device("cuda")
+    st = HostStager(dev)
+    bufs = [torch.zeros(1 << 20, device=dev), torch.zeros(1 << 20, device=dev)]
+    st.register("a", bufs)
+    acc = torch.zeros(1 << 20, device=dev)
+    for k in range(1, 6):
+        hosts = [torch.full((1 << 20,), float(k)).pin_memory(), torch.full((1 << 20,), float(-k)).pin_memory()]
+        st.prefetch("a", hosts)
+        x, y = st.acquire("a")
+        acc += x + 2 * y  # = -k
+        st.release("a")
+    torch.cuda.synchronize()
+    assert torch.all(acc == -15.0)
+    with pytest.raises(ValueError):
+        st.prefetch("a", [torch.zeros(4), torch.zeros(4)])  # not pinned
+    with pytest.raises(RuntimeError):
+        st.acquire("a")
