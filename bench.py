@@ -140,7 +140,7 @@ def gpu_arm(args):
         dist.barrier()
     from quartet_b200 import ops
     from quartet_b200.quantization import BACKWARD_SCHEMES, QUANTIZER_CLASSES, QuantizedLinear
-    from quartet_b200.shard import WgradReduceScatter
+    from quartet_b200.shard import PeerWgradScatter, WgradReduceScatter
     from quartet_b200.staging import HostStager
 
     # ---- model + data (seeded; weights identical on every rank, activations differ per rank) ----
@@ -163,7 +163,16 @@ def gpu_arm(args):
         eh = (torch.randn(TOKENS, n) * 1e-3).to(torch.bfloat16).pin_memory()
         xs_host.append(xh), es_host.append(eh)
         xs.append(xh.to(dev).requires_grad_(True)), es.append(eh.to(dev))
-    reducer = WgradReduceScatter(world) if world > 1 else None
+    # wgrad exchange across ranks: rows of each partial dW go straight from the GEMM epilogue into their
+    # owner's memory ("peer", the default), or a NCCL reduce-scatter of full partials ("nccl")
+    reducer = sink = None
+    if world > 1 and args.exchange == "peer":
+        sink = PeerWgradScatter(device=dev)
+        for lin in layers:
+            sink.prepare(lin.weight)
+            lin.wgrad_sink = sink
+    elif world > 1:
+        reducer = WgradReduceScatter(world)
 
     # ---- count launches of this library's kernels and time them per kind ----
     counts = {"n": 0}
@@ -191,6 +200,9 @@ def gpu_arm(args):
     ops.quant_bwd = wrap("quant_bwd", real["quant_bwd"], lambda x, *a, **k: ("bytes", x.numel() * (x.element_size() + 0.53125)))
     ops.quant_bwd_t = wrap("quant_bwd_t", real["quant_bwd_t"], lambda x, *a, **k: ("bytes", x.numel() * (x.element_size() + 0.53125)))
     ops.requant_t = wrap("requant_t", real["requant_t"], lambda c, *a, **k: ("bytes", c.numel() * 2 * 1.0625))
+    ops.gemm_mxfp4_tn_scatter = wrap("gemm", ops.gemm_mxfp4_tn_scatter,
+                                     lambda a_, asf, b_, *r, **k: ("flops", 2.0 * a_.shape[0] * b_.shape[0] * a_.shape[1] * 2))
+    ops.shard_reduce = wrap("shard_reduce", ops.shard_reduce, lambda ptr, n_slots, elems, *r, **k: ("bytes", (n_slots + 1) * elems * 4))
     ops.gemm_mxfp4_tn = wrap("gemm", real["gemm_mxfp4_tn"],
                              lambda a_, asf, b_, *r, **k: ("flops", 2.0 * a_.shape[0] * b_.shape[0] * a_.shape[1] * 2))
 
@@ -217,12 +229,12 @@ def gpu_arm(args):
             if reducer is not None:
                 reducer.submit(lin.weight.grad)
             if from_host:
-                sums.append(torch.stack([y.float().sum(), xs[i].grad.float().sum(), lin.weight.grad.float().sum()]))
+                sums.append([y.float().sum(), xs[i].grad.float().sum()])
                 stager.release(i)
-        if reducer is not None:
-            reducer.wait()
+        shards = reducer.wait() if reducer is not None else (sink.wait() if sink is not None else [lin.weight.grad for lin in layers])
         if from_host:
-            return torch.stack(sums).cpu()  # the step's result read back to the host
+            # the step's result read back to the host: per-layer checksums of y, dx and this rank's dw (shard)
+            return torch.stack([torch.stack(s2 + [dw.float().sum()]) for s2, dw in zip(sums, shards)]).cpu()
         return None
 
     def timed(n_steps, from_host):
@@ -270,6 +282,8 @@ def gpu_arm(args):
         a["work"] += work
         a["n"] += 1
     status = ops.device_status()
+    if sink is not None:
+        sink.close()
 
     if rank != 0:
         if world > 1:
@@ -298,14 +312,14 @@ def gpu_arm(args):
         "ms_per_step": round(ms_per_step, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "mxfp4",
         "data": "synthetic",
         "config": {"workload": WORKLOAD, "tokens_per_gpu": TOKENS, "layers": [[n_, k, n] for n_, k, n in LAYERS],
-                   "activations": "bf16", "weights": "fp32 master", "parallelism": f"dp{world} token-row shards + NCCL reduce-scatter of wgrad",
+                   "activations": "bf16", "weights": "fp32 master", "parallelism": f"dp{world} token-row shards" + ("" if world == 1 else (" + wgrad rows stored to their owner by the GEMM (peer memory)" if args.exchange == "peer" else " + NCCL reduce-scatter of wgrad")),
                    "l2": "inputs larger than L2 (>= 134 MB per operand, 3.9 GB per step)"},
         "e2e": {"value": round(flops / (e2e_ms / args.steps * 1e-3) / 1e12, 2), "unit": "TFLOP/s", "h2d_bytes_per_step": h2d,
                 "d2h_bytes_per_step": len(LAYERS) * 3 * 4, "ms_per_step": round(e2e_ms / args.steps, 3),
                 "note": "activations and grad-outputs copied from pinned host memory every step (side stream, one layer ahead of compute); weights stay resident; per-layer checksums of y, dx, dw read back"},
         "gpu_launches": launches,
         "clocks": clocks,
-        "roofline": {"bound": "tensor", "kernel": "gemm_mxfp4_kernel", "achieved": round(gemm_tflops, 1), "peak": round(4 * bf16_peak, 1),
+        "roofline": {"bound": "tensor", "kernel": "gemm_mxfp4_2cta_kernel", "achieved": round(gemm_tflops, 1), "peak": round(4 * bf16_peak, 1),
                      "unit": "TFLOP/s", "frac": round(gemm_tflops / (4 * bf16_peak), 4), "traffic": None,
                      "peak_note": f"4 x {peak_note} sustained bf16 cuBLAS rate (MXFP4:bf16 dense ratio of the tensor cores)",
                      "launches": g["n"], "avg_ms": round(g["ms"] / g["n"], 4)},
@@ -329,6 +343,7 @@ def main():
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"], help="wgrad exchange for --gpus > 1")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.impl == "reference":

@@ -131,6 +131,32 @@ int quartet_unrotate_mask(const void* g, int g_dtype, const uint8_t* mask, int64
 int quartet_dequant(const uint8_t* codes, const uint8_t* sf, int64_t rows, int64_t cols, float scale, void* out,
                     int out_dtype, quartet_stream_t stream);
 
+/*
+ * The same contraction with the fp32 result scattered by row range: rows [o * rows_per_owner,
+ * (o + 1) * rows_per_owner) of D are stored to owners[o] as a dense [rows_per_owner, N] matrix.
+ * owners is a HOST array of n_owners (<= 8) device pointers, which may be mappings of other GPUs'
+ * memory (quartet_peer_open): the weight-gradient GEMM then delivers every rank's partial rows to the
+ * rank that owns them while it computes, in place of the all-reduce torch DDP runs on full gradients
+ * in the reference (src/main.py:79-85).  M, N multiples of 256; rows_per_owner a multiple of 32.
+ */
+int quartet_gemm_mxfp4_tn_scatter(const uint8_t* a, const uint8_t* a_sf, const uint8_t* b, const uint8_t* b_sf, int64_t M,
+                                  int64_t N, int64_t K, float alpha, const uint8_t* mask, float had_scale,
+                                  void* const* owners, int32_t n_owners, int64_t rows_per_owner, quartet_stream_t stream);
+
+/* out[i] = scale * sum_s slots[s * slot_elems + i], slots added in index order. */
+int quartet_shard_reduce(const float* slots, int32_t n_slots, int64_t slot_elems, float scale, float* out,
+                         quartet_stream_t stream);
+
+/*
+ * Receive buffers other GPUs of the node can map: quartet_peer_alloc allocates `bytes` on the current
+ * device and fills 64 opaque bytes that another PROCESS passes to quartet_peer_open to obtain a
+ * pointer valid on its own device (CUDA IPC; peer access is enabled on first use).
+ */
+int quartet_peer_alloc(uint64_t bytes, void** ptr, void* handle64);
+int quartet_peer_free(void* ptr);
+int quartet_peer_open(const void* handle64, void** ptr);
+int quartet_peer_close(void* ptr);
+
 /* Host helpers for the blocked scale layout (`to_blocked`, benchmark_mxfp4.ipynb:1015-1016). */
 int64_t quartet_sf_offset(int64_t row, int64_t kblock, int64_t padded_kblocks);
 int64_t quartet_sf_bytes(int64_t rows, int64_t cols);

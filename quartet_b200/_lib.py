@@ -21,6 +21,12 @@ SIGNATURES = {
     "quartet_quant_bwd_t": (_i, [_p, _i, _i64, _i64, _f, _u32, _p, _i, _u64, _u64, _p, _p, _p, _p]),
     "quartet_requant_t": (_i, [_p, _p, _i64, _i64, _f, _f, _u32, _p, _i, _u64, _u64, _p, _p, _p, _p]),
     "quartet_gemm_mxfp4_tn": (_i, [_p, _p, _p, _p, _i64, _i64, _i64, _f, _p, _f, _p, _i, _p]),
+    "quartet_gemm_mxfp4_tn_scatter": (_i, [_p, _p, _p, _p, _i64, _i64, _i64, _f, _p, _f, _p, C.c_int32, _i64, _p]),
+    "quartet_shard_reduce": (_i, [_p, C.c_int32, _i64, _f, _p, _p]),
+    "quartet_peer_alloc": (_i, [_u64, C.POINTER(C.c_void_p), _p]),
+    "quartet_peer_free": (_i, [_p]),
+    "quartet_peer_open": (_i, [_p, C.POINTER(C.c_void_p)]),
+    "quartet_peer_close": (_i, [_p]),
     "quartet_unrotate_mask": (_i, [_p, _i, _p, _i64, _i64, _f, _p, _i, _p]),
     "quartet_dequant": (_i, [_p, _p, _i64, _i64, _f, _p, _i, _p]),
     "quartet_sf_offset": (_i64, [_i64, _i64, _i64]),

@@ -75,6 +75,15 @@ struct GemmParams {
     const uint8_t* mask;     // [M, N/8] or NULL
     float had_scale;
     int d_f32;
+    int rows_per_owner;      // > 0: output rows are scattered to per-owner destinations (two-CTA kernel only)
+};
+
+// Destinations of a scattered output: rows [o * rows_per_owner, (o + 1) * rows_per_owner) of D are
+// stored through map o, as a dense [rows_per_owner, N] fp32 matrix that may live in another GPU's
+// memory (plain TMA stores over NVLink; nothing here reads peer memory).
+constexpr int MAX_OWNERS = 8;
+struct ScatterMaps {
+    CUtensorMap m[MAX_OWNERS];
 };
 
 // ---------------------------------------------------------------------------
@@ -557,7 +566,8 @@ __device__ __forceinline__ void tile_coords(int tile, int m_pairs, int n_tiles, 
 template <int BN>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM2_THREADS, 1)
     gemm_mxfp4_2cta_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
-                           const __grid_constant__ CUtensorMap tm_d, const GemmParams p) {
+                           const __grid_constant__ CUtensorMap tm_d, const __grid_constant__ ScatterMaps sc,
+                           const GemmParams p) {
     using C = Gemm2Cfg<BN>;
     // Dynamic shared memory is the kernel's only shared memory and starts 1024-byte aligned (checked
     // below); no slack is reserved for re-aligning it, which is what makes room for a sixth stage.
@@ -793,8 +803,15 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM2_THREADS, 1)
             if (!gemm_wait(&acc_full[as], (acc_it / C::ACC_STAGES) & 1, WAIT_GEMM_ACC_FULL, dead)) break;
             if (warp == 2 && lane == 0) TRACE(9, acc_it);
             tc_fence_after();
-            const int row0 = m_blk * BM + q * 32;
-            const int64_t row = (int64_t)row0 + lane;
+            const int64_t row = (int64_t)(m_blk * BM + q * 32) + lane;
+            // where this warp's 32 rows are stored: the one output, or their owner's slice of it
+            int row0 = m_blk * BM + q * 32;
+            const CUtensorMap* tmd = &tm_d;
+            if (p.rows_per_owner > 0) {
+                const int owner = row0 / p.rows_per_owner;
+                tmd = &sc.m[owner];
+                row0 -= owner * p.rows_per_owner;
+            }
             const int n_chunks = min(BN, p.N - n0) / 32;
             uint32_t ra[32], rb[32];
             if constexpr (C::OVERLAP) {
@@ -808,13 +825,13 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM2_THREADS, 1)
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive_cluster(mapa_u32(smem_u32(&acc_empty[0]), 0));
-                if (c0 < n_chunks) epilogue_block<1>(ra, p, &tm_d, row, row0, n0 + c0 * 32, stg, n_stores, lane);
+                if (c0 < n_chunks) epilogue_block<1>(ra, p, tmd, row, row0, n0 + c0 * 32, stg, n_stores, lane);
                 if (c2 < n_chunks) tc_ld32(t0 + c2 * 32, ra);
-                if (c1 < n_chunks) epilogue_block<1>(rb, p, &tm_d, row, row0, n0 + c1 * 32, stg, n_stores, lane);
+                if (c1 < n_chunks) epilogue_block<1>(rb, p, tmd, row, row0, n0 + c1 * 32, stg, n_stores, lane);
                 if (c3 < n_chunks) tc_ld32(t0 + c3 * 32, rb);
                 tc_wait_ld();
-                if (c2 < n_chunks) epilogue_block<1>(ra, p, &tm_d, row, row0, n0 + c2 * 32, stg, n_stores, lane);
-                if (c3 < n_chunks) epilogue_block<1>(rb, p, &tm_d, row, row0, n0 + c3 * 32, stg, n_stores, lane);
+                if (c2 < n_chunks) epilogue_block<1>(ra, p, tmd, row, row0, n0 + c2 * 32, stg, n_stores, lane);
+                if (c3 < n_chunks) epilogue_block<1>(rb, p, tmd, row, row0, n0 + c3 * 32, stg, n_stores, lane);
                 // all of this tile's tensor-memory reads are complete before the warp's next arrive
                 tc_fence_before();
             } else {
@@ -823,11 +840,11 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM2_THREADS, 1)
                 for (int ch = par; ch < n_chunks; ch += 4) {
                     tc_wait_ld();
                     if (ch + 2 < n_chunks) tc_ld32(t0 + (ch + 2) * 32, rb);
-                    epilogue_block<1>(ra, p, &tm_d, row, row0, n0 + ch * 32, stg, n_stores, lane);
+                    epilogue_block<1>(ra, p, tmd, row, row0, n0 + ch * 32, stg, n_stores, lane);
                     if (ch + 2 < n_chunks) {
                         tc_wait_ld();
                         if (ch + 4 < n_chunks) tc_ld32(t0 + (ch + 4) * 32, ra);
-                        epilogue_block<1>(rb, p, &tm_d, row, row0, n0 + (ch + 2) * 32, stg, n_stores, lane);
+                        epilogue_block<1>(rb, p, tmd, row, row0, n0 + (ch + 2) * 32, stg, n_stores, lane);
                     }
                 }
                 tc_fence_before();
@@ -854,7 +871,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM2_THREADS, 1)
 }
 
 template <int BN>
-static int launch_gemm_2cta(const uint8_t* a, const uint8_t* b, void* d, const GemmParams& p0, cudaStream_t stream) {
+static int launch_gemm_2cta(const uint8_t* a, const uint8_t* b, void* d, const GemmParams& p0, cudaStream_t stream,
+                            void* const* owners = nullptr, int n_owners = 0) {
     using C = Gemm2Cfg<BN>;
     GemmParams p = p0;
     p.n_tiles = (p.N + BN - 1) / BN;
@@ -863,7 +881,18 @@ static int launch_gemm_2cta(const uint8_t* a, const uint8_t* b, void* d, const G
     if (rc) return rc;
     rc = make_tmap_2d(&tm_b, b, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, p.K / 2, p.N, p.K / 2, BK_BYTES, BN / 2, 3);
     if (rc) return rc;
-    if (p.d_f32)
+    static ScatterMaps sc;  // stays zero unless the output is scattered (then rebuilt below, per call)
+    ScatterMaps sc_call;
+    const ScatterMaps* scp = &sc;
+    if (n_owners > 0) {
+        for (int o = 0; o < n_owners; ++o)
+            if ((rc = make_tmap_2d(&sc_call.m[o], owners[o], CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, p.N, p.rows_per_owner,
+                                   (uint64_t)p.N * 4, 16, 32, 2)))
+                return rc;
+        for (int o = n_owners; o < MAX_OWNERS; ++o) sc_call.m[o] = sc_call.m[0];
+        tm_d = sc_call.m[0];
+        scp = &sc_call;
+    } else if (p.d_f32)
         rc = make_tmap_2d(&tm_d, d, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, p.N, p.M, (uint64_t)p.N * 4, 16, 32, 2);
     else
         rc = make_tmap_2d(&tm_d, d, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, p.N, p.M, (uint64_t)p.N * 2, 32, 32, 2);
@@ -897,7 +926,7 @@ static int launch_gemm_2cta(const uint8_t* a, const uint8_t* b, void* d, const G
 #ifdef QUARTET_GEMM_TRACE
     if (const char* e = getenv("QUARTET_GEMM_MAX_CLUSTERS")) clusters = clusters < atoi(e) ? clusters : atoi(e);
 #endif
-    kern<<<clusters * 2, GEMM2_THREADS, C::SMEM, stream>>>(tm_a, tm_b, tm_d, p);
+    kern<<<clusters * 2, GEMM2_THREADS, C::SMEM, stream>>>(tm_a, tm_b, tm_d, *scp, p);
 #ifdef QUARTET_GEMM_TRACE
     {
         static long long h[16][64];
@@ -998,4 +1027,36 @@ extern "C" __attribute__((visibility("default"))) int quartet_gemm_mxfp4_tn(cons
     }
     if (wide) return launch_gemm<256>(a, b, d, p, s);
     return launch_gemm<128>(a, b, d, p, s);
+}
+
+// Same contraction with the fp32 result scattered by row range: rows [o * rows_per_owner, (o + 1) *
+// rows_per_owner) go to owners[o], a dense [rows_per_owner, N] fp32 matrix (typically the slot this
+// rank owns in GPU o's receive buffer).
+extern "C" __attribute__((visibility("default"))) int quartet_gemm_mxfp4_tn_scatter(
+    const uint8_t* a, const uint8_t* a_sf, const uint8_t* b, const uint8_t* b_sf, int64_t M, int64_t N, int64_t K, float alpha,
+    const uint8_t* mask, float had_scale, void* const* owners, int32_t n_owners, int64_t rows_per_owner, quartet_stream_t stream) {
+    if (!a || !a_sf || !b || !b_sf || !owners) return fail(QUARTET_E_NULL, "a, a_sf, b, b_sf and owners must be non-NULL");
+    if (n_owners < 1 || n_owners > MAX_OWNERS) return fail(QUARTET_E_ARG, "n_owners must be 1..%d (got %d)", MAX_OWNERS, n_owners);
+    if (M < 256 || N < 256 || K < 128 || M % 256 || N % 256 || K % 128)
+        return fail(QUARTET_E_SHAPE, "scatter needs M, N multiples of 256 and K a multiple of 128 (got %lld, %lld, %lld)",
+                    (long long)M, (long long)N, (long long)K);
+    if (M > (1 << 30) || N > (1 << 30) || K > (1 << 30)) return fail(QUARTET_E_SHAPE, "extent too large");
+    if (rows_per_owner < 32 || rows_per_owner % 32 || rows_per_owner * n_owners != M)
+        return fail(QUARTET_E_SHAPE, "rows_per_owner must be a multiple of 32 with rows_per_owner * n_owners == M");
+    if (!aligned16(a) || !aligned16(b) || !aligned16(a_sf) || !aligned16(b_sf) || (mask && (reinterpret_cast<uintptr_t>(mask) & 3)))
+        return fail(QUARTET_E_ALIGN, "operands must be 16-byte aligned (mask: 4-byte)");
+    for (int o = 0; o < n_owners; ++o)
+        if (!owners[o] || !aligned16(owners[o])) return fail(QUARTET_E_ALIGN, "owners[%d] must be a 16-byte aligned device pointer", o);
+    int rc = bind_context_of(a);
+    if (rc) return rc;
+    if ((rc = check_device())) return rc;
+    GemmParams p{};
+    p.a_sf = a_sf, p.b_sf = b_sf;
+    p.M = (int)M, p.N = (int)N, p.K = (int)K;
+    p.k_chunks = (int)(K / 128);
+    p.m_tiles = (int)(M / BM);
+    p.alpha = alpha, p.mask = mask, p.had_scale = had_scale;
+    p.d_f32 = 1;
+    p.rows_per_owner = (int)rows_per_owner;
+    return launch_gemm_2cta<256>(a, b, nullptr, p, static_cast<cudaStream_t>(stream), owners, n_owners);
 }

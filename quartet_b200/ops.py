@@ -129,6 +129,65 @@ def gemm_mxfp4_tn(a, a_sf, b, b_sf, alpha=1.0, mask=None, had_scale=HAD_SCALE_BF
     return out
 
 
+def gemm_mxfp4_tn_scatter(a, a_sf, b, b_sf, owner_ptrs, rows_per_owner, alpha=1.0, mask=None, had_scale=HAD_SCALE_BF16):
+    """The fp32 product of `gemm_mxfp4_tn` with rows [o*rows_per_owner, (o+1)*rows_per_owner) stored to the
+    device address owner_ptrs[o] (a dense [rows_per_owner, N] matrix, possibly in another GPU's memory)."""
+    import ctypes as C
+
+    _need_cuda(a, a_sf, b, b_sf, mask)
+    M, K = a.shape[0], a.shape[1] * 2
+    N = b.shape[0]
+    if b.shape[1] * 2 != K:
+        raise ValueError(f"contraction extents differ: {K} vs {b.shape[1] * 2}")
+    arr = (C.c_void_p * len(owner_ptrs))(*[int(x) for x in owner_ptrs])
+    with torch.cuda.device(a.device):
+        rc = _lib.load().quartet_gemm_mxfp4_tn_scatter(_ptr(a), _ptr(a_sf), _ptr(b), _ptr(b_sf), M, N, K, alpha, _ptr(mask), had_scale,
+                                                       C.cast(arr, C.c_void_p), len(owner_ptrs), rows_per_owner, _stream())
+    _lib.check(rc, "quartet_gemm_mxfp4_tn_scatter")
+
+
+def shard_reduce(slots_ptr, n_slots, slot_elems, scale, out):
+    """out[i] = scale * sum_s slots[s*slot_elems + i]; `slots_ptr` is a device address, `out` an fp32 tensor."""
+    _need_cuda(out)
+    if out.dtype != torch.float32 or not out.is_contiguous() or out.numel() != slot_elems:
+        raise ValueError("out must be a contiguous fp32 tensor of slot_elems elements")
+    with torch.cuda.device(out.device):
+        rc = _lib.load().quartet_shard_reduce(int(slots_ptr), n_slots, slot_elems, scale, _ptr(out), _stream())
+    _lib.check(rc, "quartet_shard_reduce")
+    return out
+
+
+def peer_alloc(nbytes, device):
+    """(device address, 64-byte handle) of a buffer other processes of the node can map."""
+    import ctypes as C
+
+    ptr, handle = C.c_void_p(), C.create_string_buffer(64)
+    with torch.cuda.device(device):
+        rc = _lib.load().quartet_peer_alloc(nbytes, C.byref(ptr), C.cast(handle, C.c_void_p))
+    _lib.check(rc, "quartet_peer_alloc")
+    return ptr.value, handle.raw
+
+
+def peer_open(handle, device):
+    import ctypes as C
+
+    ptr, buf = C.c_void_p(), C.create_string_buffer(bytes(handle), 64)
+    with torch.cuda.device(device):
+        rc = _lib.load().quartet_peer_open(C.cast(buf, C.c_void_p), C.byref(ptr))
+    _lib.check(rc, "quartet_peer_open")
+    return ptr.value
+
+
+def peer_close(ptr, device):
+    with torch.cuda.device(device):
+        _lib.check(_lib.load().quartet_peer_close(int(ptr)), "quartet_peer_close")
+
+
+def peer_free(ptr, device):
+    with torch.cuda.device(device):
+        _lib.check(_lib.load().quartet_peer_free(int(ptr)), "quartet_peer_free")
+
+
 def unrotate_mask(g, mask=None, had_scale=HAD_SCALE_BF16, out_dtype=None):
     """((g * mask).view(-1, 32) @ H^T).view_as(g)"""
     _need_cuda(g, mask)

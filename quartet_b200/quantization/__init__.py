@@ -107,7 +107,8 @@ class QuantizedLinear(nn.Linear):
                         out_dtype = torch.float32
                 else:
                     out_dtype = x.dtype
-                return QuartetLinearFn.apply(x, self.weight, aq, wq, self.backward_scheme.g_quantizer, out_dtype)
+                return QuartetLinearFn.apply(x, self.weight, aq, wq, self.backward_scheme.g_quantizer, out_dtype,
+                                             getattr(self, "wgrad_sink", None))
         xq = self.activation_quantizer(x)
         wq = self.weight_quantizer(self.weight)
         return self.backward_scheme(xq, wq)

@@ -32,7 +32,7 @@ def _pad_rows(t: torch.Tensor, mult: int = 128) -> torch.Tensor:
 
 class QuartetLinearFn(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, w, a_q, w_q, g_q, out_dtype):
+    def forward(ctx, x, w, a_q, w_q, g_q, out_dtype, wgrad_sink=None):
         K = w.shape[1]
         x2 = x.reshape(-1, K)
         m_real = x2.shape[0]
@@ -45,6 +45,7 @@ class QuartetLinearFn(torch.autograd.Function):
         ctx.a_q, ctx.w_q, ctx.g_q = a_q, w_q, g_q
         ctx.x_shape, ctx.m_real = x.shape, m_real
         ctx.x_dtype, ctx.w_dtype = x.dtype, w.dtype
+        ctx.wgrad_sink, ctx.weight = wgrad_sink, w
         return y[:m_real].reshape(*x.shape[:-1], w.shape[0])
 
     @staticmethod
@@ -75,5 +76,10 @@ class QuartetLinearFn(torch.autograd.Function):
         if ctx.needs_input_grad[1]:
             etc, ets = ops.quant_bwd_t(e2, hb, rounding=rounding, seed=seeds[2], **sg)
             xtc, xts = ops.requant_t(xc, xs, 1.0, hb, rounding=rounding, seed=seeds[3], **sg)
-            dw = ops.gemm_mxfp4_tn(etc, ets, xtc, xts, alpha, mask=wm, had_scale=ctx.w_q.had_scale, out_dtype=ctx.w_dtype)
-        return dx, dw, None, None, None, None
+            sink = ctx.wgrad_sink
+            if sink is not None and sink.accepts(wc.shape[0], wc.shape[1] * 2, ctx.w_dtype):
+                # the GEMM delivers each rank's rows to their owner; the averaged shard lands in weight.grad_shard
+                sink.wgrad(ctx.weight, etc, ets, xtc, xts, alpha, wm, ctx.w_q.had_scale)
+            else:
+                dw = ops.gemm_mxfp4_tn(etc, ets, xtc, xts, alpha, mask=wm, had_scale=ctx.w_q.had_scale, out_dtype=ctx.w_dtype)
+        return dx, dw, None, None, None, None, None

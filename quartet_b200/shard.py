@@ -61,3 +61,107 @@ class WgradReduceScatter:
             torch.cuda.current_stream().wait_stream(self.stream)
         out, self.pending = self.pending, []
         return out
+
+
+class PeerWgradScatter:
+    """The weight-gradient exchange folded into the wgrad GEMM.
+
+    Rank r's GEMM stores the rows of its partial dW that rank o owns directly into slot r of a
+    receive buffer in o's memory (TMA stores over NVLink while the tiles are computed,
+    `ops.gemm_mxfp4_tn_scatter`); a one-element all-reduce on a side stream then orders "every rank's
+    GEMM has finished" before the owner sums its slots (`ops.shard_reduce`, fixed order, scaled by
+    1/world as the reference's DDP averages, src/distributed/ddp.py:43).  No gradient bytes go through a
+    library collective and no full-size partial is ever written to local memory.
+
+    Attach with `layer.wgrad_sink = sink`; the layer's backward then returns no dense weight gradient
+    and the averaged shard (rows [rank*N/world, (rank+1)*N/world)) is found in `layer.weight.grad_shard`
+    after `sink.wait()`.  Call `wait()` once per step: the two receive buffers of a layer alternate from
+    use to use, and that per-step join is what makes reusing one of them safe.
+    """
+
+    MAX_WORLD = 8
+
+    def __init__(self, group=None, device=None):
+        from . import ops
+
+        self.ops = ops
+        self.group = group
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        if dist.get_backend(group) != "nccl":
+            raise RuntimeError("PeerWgradScatter moves gradients through GPU peer memory; it needs the nccl backend")
+        if self.world > self.MAX_WORLD:
+            raise ValueError(f"at most {self.MAX_WORLD} ranks (one NVLink domain)")
+        self.device = torch.device(device if device is not None else torch.cuda.current_device())
+        self.stream = torch.cuda.Stream(device=self.device)
+        self.flag = torch.zeros(1, device=self.device)
+        self.plans = {}
+        self.pending = []
+
+    def accepts(self, rows: int, cols: int, dtype: torch.dtype) -> bool:
+        return (dtype == torch.float32 and rows % 256 == 0 and cols % 256 == 0 and rows % self.world == 0
+                and (rows // self.world) % 32 == 0)
+
+    def prepare(self, weight: torch.Tensor):
+        """Collective: allocates this layer's receive buffers and maps every peer's.  All ranks must
+        prepare their layers in the same order."""
+        key = id(weight)
+        if key in self.plans:
+            return self.plans[key]
+        rows, cols = weight.shape
+        if not self.accepts(rows, cols, weight.dtype):
+            raise ValueError(f"weight [{rows}, {cols}] {weight.dtype} cannot be scattered over {self.world} ranks")
+        rpo = rows // self.world
+        slot_bytes = rpo * cols * 4
+        mine, handles = [], []
+        for _ in range(2):
+            ptr, h = self.ops.peer_alloc(self.world * slot_bytes, self.device)
+            mine.append(ptr), handles.append(h)
+        gathered = [None] * self.world
+        dist.all_gather_object(gathered, handles, group=self.group)
+        dst, opened = [], []
+        for parity in range(2):
+            bases = []
+            for o in range(self.world):
+                if o == self.rank:
+                    bases.append(mine[parity])
+                else:
+                    p = self.ops.peer_open(gathered[o][parity], self.device)
+                    opened.append(p)
+                    bases.append(p)
+            dst.append([b + self.rank * slot_bytes for b in bases])
+        plan = {"rows": rows, "cols": cols, "rpo": rpo, "mine": mine, "dst": dst, "opened": opened, "uses": 0}
+        self.plans[key] = plan
+        return plan
+
+    def wgrad(self, weight, a, a_sf, b, b_sf, alpha, mask, had_scale):
+        plan = self.prepare(weight)
+        parity = plan["uses"] & 1
+        plan["uses"] += 1
+        self.ops.gemm_mxfp4_tn_scatter(a, a_sf, b, b_sf, plan["dst"][parity], plan["rpo"], alpha, mask=mask, had_scale=had_scale)
+        out = torch.empty(plan["rpo"], plan["cols"], dtype=torch.float32, device=self.device)
+        self.stream.wait_stream(torch.cuda.current_stream(self.device))
+        with torch.cuda.stream(self.stream):
+            dist.all_reduce(self.flag, group=self.group)  # every rank's GEMM of this layer has completed
+            self.ops.shard_reduce(plan["mine"][parity], self.world, plan["rpo"] * plan["cols"], 1.0 / self.world, out)
+        out.record_stream(self.stream)
+        weight.grad_shard = out
+        self.pending.append(out)
+        return out
+
+    def wait(self):
+        torch.cuda.current_stream(self.device).wait_stream(self.stream)
+        out, self.pending = self.pending, []
+        return out
+
+    def close(self):
+        torch.cuda.synchronize(self.device)
+        dist.barrier(group=self.group)
+        for plan in self.plans.values():
+            for p in plan["opened"]:
+                self.ops.peer_close(p, self.device)
+        dist.barrier(group=self.group)
+        for plan in self.plans.values():
+            for p in plan["mine"]:
+                self.ops.peer_free(p, self.device)
+        self.plans = {}

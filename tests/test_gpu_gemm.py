@@ -130,3 +130,38 @@ def test_layer_against_golden(ops, golden_dir):
         err = ((got - ref).norm() / ref.norm()).item()
         print(name, "rel err vs reference", err)
         assert err < 1e-5
+
+
+@pytest.mark.parametrize("owners", [1, 2, 4, 8])
+def test_gemm_scatter_equals_dense_result_and_shard_reduce_is_ordered(ops, owners):
+    """The scattered store (one GPU standing in for every owner) lands exactly the rows of the dense fp32
+    result in each owner's slot, with the fused mask + un-rotation; the slot sum is the in-order sum."""
+    m, n, k = 512, 768, 1024
+    dev, av, bv = _operands(m, n, k, seed=91)
+    gen = torch.Generator().manual_seed(92)
+    mask = torch.rand(m, n, generator=gen) < 0.9
+    pm = rm.Quantized(m, n, None, None, None, None, mask).packed_mask().cuda()
+    dense = ops.gemm_mxfp4_tn(*dev, alpha=16.0 / 9.0, mask=pm, had_scale=ops.HAD_SCALE_BF16, out_dtype=torch.float32)
+    rpo = m // owners
+    slots = torch.full((owners, rpo, n), float("nan"), device="cuda")
+    ops.gemm_mxfp4_tn_scatter(*dev, [slots[o].data_ptr() for o in range(owners)], rpo, alpha=16.0 / 9.0, mask=pm,
+                              had_scale=ops.HAD_SCALE_BF16)
+    assert torch.equal(slots.reshape(m, n), dense)
+    out = torch.empty(rpo, n, device="cuda")
+    ops.shard_reduce(slots.data_ptr(), owners, rpo * n, 1.0 / owners, out)
+    acc = slots[0].clone()
+    for o in range(1, owners):
+        acc = acc + slots[o]
+    assert torch.equal(out, acc * (1.0 / owners))
+    assert ops.device_status() == 0
+
+
+def test_gemm_scatter_rejects_bad_splits(ops):
+    dev, _, _ = _operands(512, 256, 256, seed=93)
+    buf = torch.empty(512, 256, device="cuda")
+    with pytest.raises(ValueError):
+        ops.gemm_mxfp4_tn_scatter(*dev, [buf.data_ptr()] * 3, 160)        # 3 * 160 != 512
+    with pytest.raises(ValueError):
+        ops.gemm_mxfp4_tn_scatter(*dev, [buf.data_ptr()] * 16, 32)        # more than 8 owners
+    with pytest.raises(ValueError):
+        ops.gemm_mxfp4_tn_scatter(*dev, [buf.data_ptr(), 0], 256)         # NULL owner
