@@ -166,8 +166,8 @@ def gpu_arm(args):
     # wgrad exchange across ranks: rows of each partial dW go straight from the GEMM epilogue into their
     # owner's memory ("peer", the default), or a NCCL reduce-scatter of full partials ("nccl")
     reducer = sink = None
-    if world > 1 and args.exchange == "peer":
-        sink = PeerWgradScatter(device=dev)
+    if world > 1 and args.exchange in ("peer", "copy"):
+        sink = PeerWgradScatter(device=dev, transport="store" if args.exchange == "peer" else "copy")
         for lin in layers:
             sink.prepare(lin.weight)
             lin.wgrad_sink = sink
@@ -312,7 +312,7 @@ def gpu_arm(args):
         "ms_per_step": round(ms_per_step, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "mxfp4",
         "data": "synthetic",
         "config": {"workload": WORKLOAD, "tokens_per_gpu": TOKENS, "layers": [[n_, k, n] for n_, k, n in LAYERS],
-                   "activations": "bf16", "weights": "fp32 master", "parallelism": f"dp{world} token-row shards" + ("" if world == 1 else (" + wgrad rows stored to their owner by the GEMM (peer memory)" if args.exchange == "peer" else " + NCCL reduce-scatter of wgrad")),
+                   "activations": "bf16", "weights": "fp32 master", "parallelism": f"dp{world} token-row shards" + ("" if world == 1 else {"peer": " + wgrad rows stored to their owner by the GEMM (peer memory)", "copy": " + wgrad rows pushed to their owner by the DMA engines", "nccl": " + NCCL reduce-scatter of wgrad"}[args.exchange]),
                    "l2": "inputs larger than L2 (>= 134 MB per operand, 3.9 GB per step)"},
         "e2e": {"value": round(flops / (e2e_ms / args.steps * 1e-3) / 1e12, 2), "unit": "TFLOP/s", "h2d_bytes_per_step": h2d,
                 "d2h_bytes_per_step": len(LAYERS) * 3 * 4, "ms_per_step": round(e2e_ms / args.steps, 3),
@@ -343,7 +343,7 @@ def main():
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"], help="wgrad exchange for --gpus > 1")
+    ap.add_argument("--exchange", default="peer", choices=["peer", "copy", "nccl"], help="wgrad exchange for --gpus > 1")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.impl == "reference":

@@ -156,6 +156,8 @@ int quartet_peer_alloc(uint64_t bytes, void** ptr, void* handle64);
 int quartet_peer_free(void* ptr);
 int quartet_peer_open(const void* handle64, void** ptr);
 int quartet_peer_close(void* ptr);
+/* Asynchronous device-to-device copy (DMA engines, no SM): e.g. local partial rows -> a slot of a peer's buffer. */
+int quartet_peer_copy(void* dst, const void* src, uint64_t bytes, quartet_stream_t stream);
 
 /* Host helpers for the blocked scale layout (`to_blocked`, benchmark_mxfp4.ipynb:1015-1016). */
 int64_t quartet_sf_offset(int64_t row, int64_t kblock, int64_t padded_kblocks);

@@ -184,8 +184,8 @@ __device__ __forceinline__ bool gemm_wait(uint64_t* bar, uint32_t parity, int32_
 
 // Epilogue of one 32-row x 32-column block held as one accumulator row per thread: scale, optional
 // mask + un-rotation (the 32 columns are exactly one Hadamard group), convert, stage 32 rows x 64
-// bytes in 64B-swizzled shared memory and hand them to TMA -- one store for bf16, two (16 columns
-// each) for fp32.  Two 2 KB staging buffers per warp alternate.
+// bytes in swizzled shared memory and hand them to TMA -- one store of 32 rows x 64 bytes for bf16, two
+// of 16 rows x 128 bytes for fp32.  Two 2 KB staging buffers per warp alternate.
 template <int NBUF>
 __device__ __forceinline__ void epilogue_block(const uint32_t (&r)[32], const GemmParams& p, const CUtensorMap* tm_d,
                                                int64_t row, int row0, int col, uint8_t* stg, uint32_t& n_stores, int lane) {
@@ -201,20 +201,23 @@ __device__ __forceinline__ void epilogue_block(const uint32_t (&r)[32], const Ge
         for (int i = 0; i < 32; ++i) v[i] *= p.had_scale;
     }
     if (p.d_f32) {
+        // two stores of 16 rows x 128 bytes (128B-swizzled staging): full 128-byte row segments, which is
+        // what keeps stores to another GPU's memory efficient on NVLink
 #pragma unroll
         for (int hf = 0; hf < 2; ++hf, ++n_stores) {
             uint8_t* buf = stg + (NBUF == 2 ? (n_stores & 1) * 2048 : 0);
             if (lane == 0) { if (NBUF == 2) bulk_wait_read1(); else bulk_wait_read0(); }
             __syncwarp();
-            uint8_t* dst = buf + lane * 64;
+            if ((lane >> 4) == hf) {
+                uint8_t* dst = buf + (lane & 15) * 128;
 #pragma unroll
-            for (int j = 0; j < 4; ++j)
-                *reinterpret_cast<float4*>(dst + ((j ^ ((lane >> 1) & 3)) << 4)) =
-                    make_float4(v[16 * hf + 4 * j], v[16 * hf + 4 * j + 1], v[16 * hf + 4 * j + 2], v[16 * hf + 4 * j + 3]);
+                for (int j = 0; j < 8; ++j)
+                    *reinterpret_cast<float4*>(dst + ((j ^ (lane & 7)) << 4)) = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+            }
             fence_proxy_async_smem();
             __syncwarp();
             if (lane == 0) {
-                tma_store_2d(tm_d, col + 16 * hf, row0, buf);
+                tma_store_2d(tm_d, col, row0 + 16 * hf, buf);
                 bulk_commit();
             }
         }
@@ -887,13 +890,13 @@ static int launch_gemm_2cta(const uint8_t* a, const uint8_t* b, void* d, const G
     if (n_owners > 0) {
         for (int o = 0; o < n_owners; ++o)
             if ((rc = make_tmap_2d(&sc_call.m[o], owners[o], CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, p.N, p.rows_per_owner,
-                                   (uint64_t)p.N * 4, 16, 32, 2)))
+                                   (uint64_t)p.N * 4, 32, 16, 3)))
                 return rc;
         for (int o = n_owners; o < MAX_OWNERS; ++o) sc_call.m[o] = sc_call.m[0];
         tm_d = sc_call.m[0];
         scp = &sc_call;
     } else if (p.d_f32)
-        rc = make_tmap_2d(&tm_d, d, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, p.N, p.M, (uint64_t)p.N * 4, 16, 32, 2);
+        rc = make_tmap_2d(&tm_d, d, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, p.N, p.M, (uint64_t)p.N * 4, 32, 16, 3);
     else
         rc = make_tmap_2d(&tm_d, d, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, p.N, p.M, (uint64_t)p.N * 2, 32, 32, 2);
     if (rc) return rc;
@@ -961,7 +964,7 @@ static int launch_gemm(const uint8_t* a, const uint8_t* b, void* d, const GemmPa
     rc = make_tmap_2d(&tm_b, b, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, p.K / 2, p.N, p.K / 2, BK_BYTES, p.N < BN ? p.N : BN, 3);
     if (rc) return rc;
     if (p.d_f32)
-        rc = make_tmap_2d(&tm_d, d, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, p.N, p.M, (uint64_t)p.N * 4, 16, 32, 2);
+        rc = make_tmap_2d(&tm_d, d, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, p.N, p.M, (uint64_t)p.N * 4, 32, 16, 3);
     else
         rc = make_tmap_2d(&tm_d, d, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, p.N, p.M, (uint64_t)p.N * 2, 32, 32, 2);
     if (rc) return rc;

@@ -85,3 +85,9 @@ extern "C" __attribute__((visibility("default"))) int quartet_peer_close(void* p
     if (!ptr) return QUARTET_OK;
     return check_cuda(cudaIpcCloseMemHandle(ptr), "cudaIpcCloseMemHandle");
 }
+// Device-to-device copy on the DMA engines (no SM is used): local rows -> a slot in a peer's buffer.
+extern "C" __attribute__((visibility("default"))) int quartet_peer_copy(void* dst, const void* src, uint64_t bytes, quartet_stream_t stream) {
+    if (!dst || !src) return fail(QUARTET_E_NULL, "dst and src must be non-NULL");
+    if (bytes == 0) return QUARTET_OK;
+    return check_cuda(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDefault, static_cast<cudaStream_t>(stream)), "cudaMemcpyAsync (peer copy)");
+}

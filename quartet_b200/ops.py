@@ -183,6 +183,12 @@ def peer_close(ptr, device):
         _lib.check(_lib.load().quartet_peer_close(int(ptr)), "quartet_peer_close")
 
 
+def peer_copy(dst_ptr, src_ptr, nbytes, device):
+    """Asynchronous copy between device addresses on the current stream (DMA engines, no SM)."""
+    with torch.cuda.device(device):
+        _lib.check(_lib.load().quartet_peer_copy(int(dst_ptr), int(src_ptr), nbytes, _stream()), "quartet_peer_copy")
+
+
 def peer_free(ptr, device):
     with torch.cuda.device(device):
         _lib.check(_lib.load().quartet_peer_free(int(ptr)), "quartet_peer_free")

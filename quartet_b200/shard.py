@@ -81,9 +81,12 @@ class PeerWgradScatter:
 
     MAX_WORLD = 8
 
-    def __init__(self, group=None, device=None):
+    def __init__(self, group=None, device=None, transport: str = "store"):
         from . import ops
 
+        if transport not in ("store", "copy"):
+            raise ValueError("transport is 'store' (GEMM epilogue stores to peers) or 'copy' (DMA engines push local rows)")
+        self.transport = transport
         self.ops = ops
         self.group = group
         self.world = dist.get_world_size(group)
@@ -138,10 +141,22 @@ class PeerWgradScatter:
         plan = self.prepare(weight)
         parity = plan["uses"] & 1
         plan["uses"] += 1
-        self.ops.gemm_mxfp4_tn_scatter(a, a_sf, b, b_sf, plan["dst"][parity], plan["rpo"], alpha, mask=mask, had_scale=had_scale)
+        dense = None
+        if self.transport == "store":
+            self.ops.gemm_mxfp4_tn_scatter(a, a_sf, b, b_sf, plan["dst"][parity], plan["rpo"], alpha, mask=mask, had_scale=had_scale)
+        else:
+            dense = self.ops.gemm_mxfp4_tn(a, a_sf, b, b_sf, alpha, mask=mask, had_scale=had_scale, out_dtype=torch.float32)
         out = torch.empty(plan["rpo"], plan["cols"], dtype=torch.float32, device=self.device)
         self.stream.wait_stream(torch.cuda.current_stream(self.device))
         with torch.cuda.stream(self.stream):
+            if dense is not None:
+                # the DMA engines push each owner's rows while the compute stream moves on; peers are
+                # visited starting after this rank so that no two ranks target one GPU at the same time
+                slot_bytes = plan["rpo"] * plan["cols"] * 4
+                for step in range(self.world):
+                    o = (self.rank + 1 + step) % self.world
+                    self.ops.peer_copy(plan["dst"][parity][o], dense.data_ptr() + o * slot_bytes, slot_bytes, self.device)
+                dense.record_stream(self.stream)
             dist.all_reduce(self.flag, group=self.group)  # every rank's GEMM of this layer has completed
             self.ops.shard_reduce(plan["mine"][parity], self.world, plan["rpo"] * plan["cols"], 1.0 / self.world, out)
         out.record_stream(self.stream)

@@ -39,23 +39,24 @@ def main():
         lin(x).backward(e)
 
     reducer = WgradReduceScatter(world)
-    sink = PeerWgradScatter()
-    shards = []
-    for step in range(3):  # three steps: both receive buffers of the layer get reused
-        run(None)
-        reducer.submit(lin.weight.grad)
-        want = reducer.wait()[0]
-        run(sink)
-        assert lin.weight.grad is None
-        got = sink.wait()[0]
-        assert got is lin.weight.grad_shard
-        torch.cuda.synchronize()
-        err = ((got - want).abs().max() / want.abs().max()).item()
-        assert err < 1e-6, (step, err)  # same addends, different summation order
-        shards.append(got.clone())
-    assert torch.equal(shards[0], shards[1]) and torch.equal(shards[1], shards[2])  # deterministic
-    assert ops.device_status() == 0
-    sink.close()
+    for transport in ("store", "copy"):  # rows stored by the GEMM epilogue / pushed by the DMA engines
+        sink = PeerWgradScatter(transport=transport)
+        shards = []
+        for step in range(3):  # three steps: both receive buffers of the layer get reused
+            run(None)
+            reducer.submit(lin.weight.grad)
+            want = reducer.wait()[0]
+            run(sink)
+            assert lin.weight.grad is None
+            got = sink.wait()[0]
+            assert got is lin.weight.grad_shard
+            torch.cuda.synchronize()
+            err = ((got - want).abs().max() / want.abs().max()).item()
+            assert err < 1e-6, (transport, step, err)  # same addends, different summation order
+            shards.append(got.clone())
+        assert torch.equal(shards[0], shards[1]) and torch.equal(shards[1], shards[2])  # deterministic
+        assert ops.device_status() == 0
+        sink.close()
     dist.destroy_process_group()
     print(f"rank {rank} ok", flush=True)
 
