@@ -201,13 +201,14 @@ __device__ __forceinline__ void absmax_quantize_group(const float (&w)[32], floa
                                                       uint32_t (&words)[4], int& e8m0) {
     float amax = 0.f;
 #pragma unroll
-    for (int i = 0; i < 32; ++i) amax = fmaxf(amax, fabsf(w[i]));
+    for (int i = 0; i < 16; ++i) amax = max3_abs(amax, w[2 * i], w[2 * i + 1]);
     amax *= h;  // max |h w| = h max|w|  (h > 0, rounding is monotone)
     const int eb = exp_field(amax);
     e8m0 = max(eb - 2, 0);
     if (ROUND == 1 /* QUARTET_ROUND_SR_PHILOX */) {
         const bool zero = eb < 3;
         const float c = zero ? 0.f : (0.75f * h) * pow2_biased(254 - e8m0);
+        const f32x2_t c2 = pack2(c, c);
 #pragma unroll
         for (int j = 0; j < 2; ++j) {
             const uint64_t ctr = 2 * g + j;
@@ -216,7 +217,10 @@ __device__ __forceinline__ void absmax_quantize_group(const float (&w)[32], floa
 #pragma unroll
             for (int wd = 0; wd < 4; ++wd) {
                 const int i = 16 * j + 4 * wd;
-                const uint32_t r16 = cvt_rs_e2m1x4(w[i] * c, w[i + 1] * c, w[i + 2] * c, w[i + 3] * c, r.w[wd]);
+                float x0, x1, x2, x3;
+                unpack2(mul2(pack2(w[i], w[i + 1]), c2), x0, x1);
+                unpack2(mul2(pack2(w[i + 2], w[i + 3]), c2), x2, x3);
+                const uint32_t r16 = cvt_rs_e2m1x4(x0, x1, x2, x3, r.w[wd]);
                 if (wd & 1)
                     words[2 * j + (wd >> 1)] = (words[2 * j + (wd >> 1)] | (r16 << 16)) ^ flip[2 * j + (wd >> 1)];
                 else

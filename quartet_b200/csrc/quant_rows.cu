@@ -106,8 +106,16 @@ __global__ void __launch_bounds__(ROWS_THREADS, F32 ? 3 : 4) quant_rows_kernel(c
         const float x0 = w[0];
         float sumsq = 0.f;
         if (KIND == KIND_QUEST) {
+            // two interleaved partial sums (even / odd elements) in one packed accumulator
+            f32x2_t acc = pack2(0.f, 0.f);
 #pragma unroll
-            for (int i = 0; i < 32; ++i) sumsq = fmaf(w[i], w[i], sumsq);
+            for (int i = 0; i < 16; ++i) {
+                const f32x2_t pr = pack2(w[2 * i], w[2 * i + 1]);
+                acc = fma2(pr, pr, acc);
+            }
+            float s_even, s_odd;
+            unpack2(acc, s_even, s_odd);
+            sumsq = s_even + s_odd;
         }
         wht32(w);
 
@@ -122,8 +130,9 @@ __global__ void __launch_bounds__(ROWS_THREADS, F32 ? 3 : 4) quant_rows_kernel(c
             e8m0 = exp_field(scales);
             const float c = h * pow2_biased(254 - e8m0);  // h * 2^-e
             float v[32];
+            const f32x2_t c2 = pack2(c, c);
 #pragma unroll
-            for (int i = 0; i < 32; ++i) v[i] = w[i] * c;
+            for (int i = 0; i < 16; ++i) unpack2(mul2(pack2(w[2 * i], w[2 * i + 1]), c2), v[2 * i], v[2 * i + 1]);
 #pragma unroll
             for (int q = 0; q < 4; ++q) words[q] = cvt_e2m1x8_rn(&v[8 * q]);
             // (the reference gives exact zeros a minus sign, `v > 0 ? + : -`; here +0 stays +0)
