@@ -67,6 +67,19 @@ int check_device() {
     return cached_ok ? QUARTET_OK : fail(QUARTET_E_DEVICE, "device %d is sm_%d%d; this library is built for sm_100a only", dev, major, minor);
 }
 
+int device_sm_count(int* sms) {
+    static thread_local int cached_dev = -1, cached_sms = 0;
+    int dev = 0;
+    int rc = check_cuda(cudaGetDevice(&dev), "cudaGetDevice");
+    if (rc) return rc;
+    if (dev != cached_dev) {
+        if ((rc = check_cuda(cudaDeviceGetAttribute(&cached_sms, cudaDevAttrMultiProcessorCount, dev), "cudaDeviceGetAttribute"))) return rc;
+        cached_dev = dev;
+    }
+    *sms = cached_sms;
+    return QUARTET_OK;
+}
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);

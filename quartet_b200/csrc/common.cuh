@@ -17,6 +17,7 @@ int fail(int code, const char* fmt, ...);  // records the thread-local error str
 int check_cuda(cudaError_t e, const char* what);
 int check_device();                          // QUARTET_OK iff the current device is sm_100
 int bind_context_of(const void* ptr);        // make the context of ptr's device current if the thread has none
+int device_sm_count(int* sms);               // SMs of the current device (cached per thread)
 
 // 2-D row-major tensor map over bytes/elements.  `swizzle`: 0 none, 1 = 32B, 2 = 64B, 3 = 128B.
 int make_tmap_2d(CUtensorMap* map, const void* base, CUtensorMapDataType dt, int elem_bytes, uint64_t inner,

@@ -41,9 +41,8 @@ extern "C" __attribute__((visibility("default"))) int quartet_shard_reduce(const
     int rc = bind_context_of(out);
     if (rc) return rc;
     if ((rc = check_device())) return rc;
-    int dev = 0, sms = 0;
-    if ((rc = check_cuda(cudaGetDevice(&dev), "cudaGetDevice"))) return rc;
-    if ((rc = check_cuda(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev), "cudaDeviceGetAttribute"))) return rc;
+    int sms = 0;
+    if ((rc = device_sm_count(&sms))) return rc;
     const int64_t vec4 = slot_elems / 4;
     int64_t blocks = (vec4 + 255) / 256;
     const int64_t cap = (int64_t)sms * 8;  // a whole number of waves of 8 CTAs per SM
