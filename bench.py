@@ -34,6 +34,26 @@ WORKLOAD = "llama7b_linears_16384tok"
 METRIC = "quantized_linear_fwd_bwd_tflops"
 
 
+# DRAM traffic of the GEMM, from the ncu capture summarised in profiles/gemm_mxfp4_2cta_8192x8192x4096.md
+# (dram__bytes_read.sum + dram__bytes_write.sum of one launch).  The bench's launches are larger than the
+# capture rule allows, so the captured traffic is scaled by algorithmic bytes (operands + scales + result).
+NCU_GEMM_CAPTURE = {"m": 8192, "n": 8192, "k": 4096, "out_bytes": 2, "dram_bytes": 39.87e6 + 90.74e6}
+
+
+def gemm_algorithmic_bytes(m, n, k, out_bytes):
+    return (m + n) * k * (0.5 + 1.0 / 32.0) + m * n * out_bytes
+
+
+def gemm_traffic_per_launch(tokens):
+    """Average over the 12 GEMM launches of a step (forward and dgrad write bf16, wgrad fp32)."""
+    cap = NCU_GEMM_CAPTURE
+    ratio = cap["dram_bytes"] / gemm_algorithmic_bytes(cap["m"], cap["n"], cap["k"], cap["out_bytes"])
+    alg = 0.0
+    for _, k, n in LAYERS:
+        alg += gemm_algorithmic_bytes(tokens, n, k, 2) + gemm_algorithmic_bytes(tokens, k, n, 2) + gemm_algorithmic_bytes(n, k, tokens, 4)
+    return ratio * alg / (3 * len(LAYERS)), alg / (3 * len(LAYERS))
+
+
 def layer_flops(m):
     return sum(6.0 * m * k * n for _, k, n in LAYERS)
 
@@ -320,7 +340,8 @@ def gpu_arm(args):
         "gpu_launches": launches,
         "clocks": clocks,
         "roofline": {"bound": "tensor", "kernel": "gemm_mxfp4_2cta_kernel", "achieved": round(gemm_tflops, 1), "peak": round(4 * bf16_peak, 1),
-                     "unit": "TFLOP/s", "frac": round(gemm_tflops / (4 * bf16_peak), 4), "traffic": None,
+                     "unit": "TFLOP/s", "frac": round(gemm_tflops / (4 * bf16_peak), 4), "traffic": round(gemm_traffic_per_launch(TOKENS)[0]),
+                     "traffic_note": "DRAM bytes per launch: ncu capture of 8192x8192x4096 (130.6 MB) scaled by algorithmic bytes to the step's average launch (%d MB algorithmic)" % round(gemm_traffic_per_launch(TOKENS)[1] / 1e6),
                      "peak_note": f"4 x {peak_note} sustained bf16 cuBLAS rate (MXFP4:bf16 dense ratio of the tensor cores)",
                      "launches": g["n"], "avg_ms": round(g["ms"] / g["n"], 4)},
         "roofline_quantizers": {"bound": "hbm", "achieved": round(q_gbs, 1), "peak": hbm_peak, "unit": "GB/s", "frac": round(q_gbs / hbm_peak, 4),

@@ -14,6 +14,7 @@ import sys
 import torch
 import torch.nn as nn
 
+from .. import ops
 from .backward import BACKWARD_SCHEMES, EW_EtX_Scheme, QEQWtt_QEtQXtt_Scheme
 from .fused import QuartetLinearFn
 from .quantizers import (AlbertTsengQuantizer, AlignedAlbertTsengQuantizer, BaseQuantizer, NoQuantizer,
@@ -94,6 +95,23 @@ class QuantizedLinear(nn.Linear):
             and self.out_features % 128 == 0
             and x.dtype in (torch.bfloat16, torch.float32)
         )
+
+    def export_mxfp4(self):
+        """The forward-quantized weight as real MXFP4: (codes uint8 [N, K/2], scales E8M0 uint8 in the
+        blocked 128 x 4 layout, had_scale).  The values are in the rotated basis (groups of 32 along K
+        multiplied by the forward Hadamard matrix), i.e. exactly the B operand of the forward GEMM --
+        the layout a block-scaled MXFP4 inference GEMM consumes (`to_blocked`,
+        notebooks/benchmark_mxfp4.ipynb:1015-1016 of the reference); the reference itself only
+        checkpoints fp32 weights (src/optim/utils.py:245-256)."""
+        wq = self.weight_quantizer
+        if type(wq) is not QuestMXFP4Quantizer or not self.weight.is_cuda:
+            raise RuntimeError("export_mxfp4 needs a QuestMXFP4Quantizer weight quantizer and a CUDA weight")
+        wq._see(self.weight)
+        if wq._sign_word() != 0:
+            raise RuntimeError("the forward rotation carries a sign vector; only the plain Hadamard rotation is exported")
+        with torch.no_grad():
+            codes, sf, _ = ops.quant_fwd(self.weight.detach().contiguous(), wq.had_scale, ops.QUEST_GAUSSIAN_SCALE, return_mask=False)
+        return codes, sf, wq.had_scale
 
     def forward(self, x):
         if self._fusable(x):

@@ -34,7 +34,7 @@ def rotary(q, k):
 
 
 class Block(nn.Module):
-    def __init__(self, Q, d, n_head, hidden, gkw):
+    def __init__(self, Q, d, n_head, hidden, gkw, n_kv_head=None):
         super().__init__()
 
         def lin(i, o):
@@ -47,28 +47,35 @@ class Block(nn.Module):
             )
 
         self.n_head, self.hidden = n_head, hidden
+        # grouped-query attention when n_kv_head < n_head (the Llama-3 shape: qkv is d + 2 d n_kv/n_head wide)
+        self.n_kv_head = n_kv_head or n_head
+        self.kv_dim = d // n_head * self.n_kv_head
         self.ln1, self.ln2 = RMSNorm(d), RMSNorm(d)
-        self.c_attn, self.attn_proj = lin(d, 3 * d), lin(d, d)
+        self.c_attn, self.attn_proj = lin(d, d + 2 * self.kv_dim), lin(d, d)
         self.w12, self.c_proj = lin(d, 2 * hidden), lin(hidden, d)
 
     def forward(self, x):
         b, t, d = x.shape
-        q, k, v = self.c_attn(self.ln1(x)).split(d, dim=2)
-        q, k, v = (z.view(b, t, self.n_head, d // self.n_head).transpose(1, 2) for z in (q, k, v))
+        hd = d // self.n_head
+        q, k, v = self.c_attn(self.ln1(x)).split([d, self.kv_dim, self.kv_dim], dim=2)
+        q = q.view(b, t, self.n_head, hd).transpose(1, 2)
+        k, v = (z.view(b, t, self.n_kv_head, hd).transpose(1, 2) for z in (k, v))
         q, k = rotary(q, k)
-        y = F.scaled_dot_product_attention(q, k, v, is_causal=True).transpose(1, 2).reshape(b, t, d)
+        y = F.scaled_dot_product_attention(q, k, v, is_causal=True, enable_gqa=self.n_kv_head != self.n_head)
+        y = y.transpose(1, 2).reshape(b, t, d)
         x = x + self.attn_proj(y)
         up, gate = self.w12(self.ln2(x)).split(self.hidden, dim=-1)
         return x + self.c_proj(F.silu(up) * gate)
 
 
 class TinyLlama(nn.Module):
-    def __init__(self, Q, vocab=512, d=256, n_layer=2, n_head=2, multiple_of=128, gkw=None):
+    def __init__(self, Q, vocab=512, d=256, n_layer=2, n_head=2, multiple_of=128, gkw=None, n_kv_head=None):
         super().__init__()
         hidden = int(2 * 4 * d / 3)
         hidden = multiple_of * ((hidden + multiple_of - 1) // multiple_of)
         self.wte = nn.Embedding(vocab, d)
-        self.blocks = nn.ModuleList(Block(Q, d, n_head, hidden, gkw or {"stochastic": True, "rerotate": "signs"}) for _ in range(n_layer))
+        self.blocks = nn.ModuleList(Block(Q, d, n_head, hidden, gkw or {"stochastic": True, "rerotate": "signs"}, n_kv_head)
+                                    for _ in range(n_layer))
         self.ln_f, self.lm_head = RMSNorm(d), nn.Linear(d, vocab, bias=False)
         for n_, p in self.named_parameters():
             if p.dim() == 2:

@@ -63,3 +63,31 @@ def test_training_reduces_loss(Q):
     assert losses[-1] < 0.7 * losses[0]
     assert list(model.blocks[0].c_attn.state_dict().keys()) == ["weight"]
     assert ops.device_status() == 0
+
+
+def test_grouped_query_block_trains_and_exports_weights(Q):
+    """Llama-3 style grouped-query attention (4 query heads, 2 key/value heads: qkv is 512 + 2 * 256 wide)
+    and the MXFP4 export of a trained layer's weight."""
+    from quartet_b200 import ops
+
+    torch.manual_seed(2)
+    model = TinyLlama(Q, d=512, n_head=4, n_kv_head=2, n_layer=1).cuda()
+    assert model.blocks[0].c_attn.out_features == 1024
+    opt = torch.optim.AdamW(model.parameters(), lr=3e-3)
+    idx = torch.randint(0, 512, (4, 128), device="cuda")
+    tgt = torch.roll(idx, -1, 1)
+    losses = []
+    for _ in range(20):
+        losses.append(_step(model, idx, tgt).item())
+        opt.step()
+    assert losses[-1] < 0.8 * losses[0]
+    lin = model.blocks[0].c_attn
+    codes, sf, had_scale = lin.export_mxfp4()
+    assert codes.shape == (1024, 256) and codes.dtype == torch.uint8 and sf.numel() == ops.sf_bytes(1024, 512)
+    # the exported operand reproduces the layer's forward: y = Q(x) . export^T
+    x = torch.randn(256, 512, device="cuda", dtype=torch.bfloat16)
+    with torch.no_grad():
+        want = lin(x)
+    xc, xs, _ = ops.quant_fwd(x, lin.activation_quantizer.had_scale, ops.QUEST_GAUSSIAN_SCALE, return_mask=False)
+    y = ops.gemm_mxfp4_tn(xc, xs, codes, sf, 1.0, out_dtype=torch.bfloat16)
+    assert torch.equal(y, want)
