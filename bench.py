@@ -219,6 +219,7 @@ def gpu_arm(args):
     ops.quant_fwd = wrap("quant_fwd", real["quant_fwd"], q_bytes(0.53125, 0.125))
     ops.quant_bwd = wrap("quant_bwd", real["quant_bwd"], lambda x, *a, **k: ("bytes", x.numel() * (x.element_size() + 0.53125)))
     ops.quant_bwd_t = wrap("quant_bwd_t", real["quant_bwd_t"], lambda x, *a, **k: ("bytes", x.numel() * (x.element_size() + 0.53125)))
+    ops.quant_bwd_dual = wrap("quant_bwd_dual", ops.quant_bwd_dual, lambda x, *a, **k: ("bytes", x.numel() * (x.element_size() + 2 * 0.53125)))
     ops.requant_t = wrap("requant_t", real["requant_t"], lambda c, *a, **k: ("bytes", c.numel() * 2 * 1.0625))
     ops.gemm_mxfp4_tn_scatter = wrap("gemm", ops.gemm_mxfp4_tn_scatter,
                                      lambda a_, asf, b_, *r, **k: ("flops", 2.0 * a_.shape[0] * b_.shape[0] * a_.shape[1] * 2))

@@ -92,6 +92,16 @@ int quartet_quant_bwd_t(const void* x, int x_dtype, int64_t rows, int64_t cols, 
                         uint8_t* codes_t, uint8_t* sf_t, quartet_stream_t stream);
 
 /*
+ * Q(E) and Q(E^T) from one read of E (both are needed by every backward pass, backward.py:72 and :81
+ * of the reference): codes/sf are exactly what quartet_quant_bwd(x, ..., seed_rows) writes and
+ * codes_t/sf_t exactly what quartet_quant_bwd_t(x, ..., seed_t) writes.  rows and cols multiples of 128;
+ * rounding 0 (nearest) or 1 (own Philox stream).
+ */
+int quartet_quant_bwd_dual(const void* x, int x_dtype, int64_t rows, int64_t cols, float had_scale, uint32_t signs,
+                           const uint32_t* signs_dev, int rounding, uint64_t seed_rows, uint64_t seed_t, uint64_t offset,
+                           uint8_t* codes, uint8_t* sf, uint8_t* codes_t, uint8_t* sf_t, quartet_stream_t stream);
+
+/*
  * De-quantize + transpose + backward-quantize of an MXFP4 tensor.
  * Replaces `g_quantizer(w.T.contiguous())` / `g_quantizer(x.reshape(M,-1).T.contiguous())`
  * (backward.py:73,82) on the saved forward-quantized operands; contract = backward_qt_bf16

@@ -19,6 +19,7 @@ SIGNATURES = {
     "quartet_quant_fwd": (_i, [_p, _i, _i64, _i64, _f, _f, _p, _p, _p, _p]),
     "quartet_quant_bwd": (_i, [_p, _i, _i64, _i64, _f, _u32, _p, _i, _u64, _u64, _p, _p, _p, _p]),
     "quartet_quant_bwd_t": (_i, [_p, _i, _i64, _i64, _f, _u32, _p, _i, _u64, _u64, _p, _p, _p, _p]),
+    "quartet_quant_bwd_dual": (_i, [_p, _i, _i64, _i64, _f, _u32, _p, _i, _u64, _u64, _u64, _p, _p, _p, _p, _p]),
     "quartet_requant_t": (_i, [_p, _p, _i64, _i64, _f, _f, _u32, _p, _i, _u64, _u64, _p, _p, _p, _p]),
     "quartet_gemm_mxfp4_tn": (_i, [_p, _p, _p, _p, _i64, _i64, _i64, _f, _p, _f, _p, _i, _p]),
     "quartet_gemm_mxfp4_tn_scatter": (_i, [_p, _p, _p, _p, _i64, _i64, _i64, _f, _p, _f, _p, C.c_int32, _i64, _p]),

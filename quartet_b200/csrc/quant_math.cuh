@@ -82,6 +82,30 @@ __device__ __forceinline__ void unpack_bf16x8(const uint4& q, float* out) {
     }
 }
 
+// One group of 32 consecutive row elements out of a 128-row tile that TMA laid down as 128-byte-wide
+// boxes (128 rows x 128 B each, 128B swizzle: 16-byte chunk c of row r sits at chunk c ^ (r & 7)).
+// `gk` = group index within the tile row (0..3).
+template <bool F32>
+__device__ __forceinline__ void load_row_group(const uint8_t* s_in, int row, int gk, float (&w)[32]) {
+    constexpr int BOX = 128 * 128;
+    if (F32) {
+        const uint8_t* base = s_in + gk * BOX + row * 128;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const float4 q = *reinterpret_cast<const float4*>(base + ((j ^ (row & 7)) << 4));
+            w[4 * j] = q.x, w[4 * j + 1] = q.y, w[4 * j + 2] = q.z, w[4 * j + 3] = q.w;
+        }
+    } else {
+        const uint8_t* base = s_in + (gk >> 1) * BOX + row * 128;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int chunk = (gk & 1) * 4 + j;
+            const uint4 q = *reinterpret_cast<const uint4*>(base + ((chunk ^ (row & 7)) << 4));
+            unpack_bf16x8(q, &w[8 * j]);
+        }
+    }
+}
+
 // ---------------------------------------------------------------------------
 // Philox4x32-10 (Salmon et al. 2011), word order as in triton/language/random.py:13-41.
 // ---------------------------------------------------------------------------

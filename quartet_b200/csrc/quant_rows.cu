@@ -85,22 +85,7 @@ __global__ void __launch_bounds__(ROWS_THREADS, F32 ? 3 : 4) quant_rows_kernel(c
     for (int it = 0; it < 2; ++it) {
         const int gk = (warp >> 2) * 2 + it;  // group within the tile row, 0..3
         float w[32];
-        if (F32) {
-            const uint8_t* base = s_in + gk * BOX_BYTES + row * 128;
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                const float4 q = *reinterpret_cast<const float4*>(base + ((j ^ (row & 7)) << 4));
-                w[4 * j] = q.x, w[4 * j + 1] = q.y, w[4 * j + 2] = q.z, w[4 * j + 3] = q.w;
-            }
-        } else {
-            const uint8_t* base = s_in + (gk >> 1) * BOX_BYTES + row * 128;
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                const int chunk = (gk & 1) * 4 + j;
-                const uint4 q = *reinterpret_cast<const uint4*>(base + ((chunk ^ (row & 7)) << 4));
-                unpack_bf16x8(q, &w[8 * j]);
-            }
-        }
+        load_row_group<F32>(s_in, row, gk, w);
         // statistics that do not need the rotated values: sum_j xh_j = 32 h x_0 (only row 0 of the
         // Sylvester matrix has a non-zero column sum) and sum_j xh_j^2 = 32 h^2 sum_i x_i^2 (Parseval).
         const float x0 = w[0];

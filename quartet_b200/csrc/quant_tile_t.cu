@@ -31,6 +31,10 @@ struct TileTParams {
     const uint32_t* signs_dev;
     uint64_t seed, offset;
     const float* noise;
+    // dual mode: the row-wise quantization of the same source, from the same tile in shared memory
+    uint8_t* sf_rows;
+    int64_t sf_rows_blocks_per_rowblock;  // pad4(cols/32) / 4
+    uint64_t seed_rows;
 };
 
 constexpr int TT = 128, TT_THREADS = 256;
@@ -39,15 +43,18 @@ template <int SRC>
 __host__ __device__ constexpr int tile_in_bytes() {
     return SRC == SRC_BF16 ? TT * TT * 2 : (SRC == SRC_F32 ? TT * TT * 4 : TT * TT / 2 + 512);
 }
-template <int SRC>
+template <int SRC, bool DUAL>
 constexpr int tile_smem_bytes() {
-    return tile_in_bytes<SRC>() + TT * 64 + 512 + 64 + 1024;
+    return tile_in_bytes<SRC>() + (DUAL ? 2 : 1) * (TT * 64 + 512) + 64 + 1024;
 }
 
-template <int SRC, int ROUND>
-__global__ void __launch_bounds__(TT_THREADS, 4) quant_tile_t_kernel(const __grid_constant__ CUtensorMap tm_in,
-                                                                    const __grid_constant__ CUtensorMap tm_out,
-                                                                    const TileTParams p) {
+// DUAL: besides the quantized transpose, the kernel also emits the row-wise quantization of the same
+// tile (what quartet_quant_bwd computes, bit for bit, with its own seed), so that the backward pass
+// reads the output-gradient once for Q(E) and Q(E^T).
+template <int SRC, int ROUND, bool DUAL>
+__global__ void __launch_bounds__(TT_THREADS, (SRC == SRC_F32 && DUAL) ? 2 : 4)
+    quant_tile_t_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant__ CUtensorMap tm_out,
+                        const __grid_constant__ CUtensorMap tm_rows, const TileTParams p) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     constexpr int IN_BYTES = tile_in_bytes<SRC>();
@@ -55,7 +62,9 @@ __global__ void __launch_bounds__(TT_THREADS, 4) quant_tile_t_kernel(const __gri
     uint8_t* s_in = smem;
     uint8_t* s_codes = smem + IN_BYTES;   // [128 out rows][64 B]
     uint8_t* s_sf = s_codes + TT * 64;    // 512 B
-    uint64_t* bar = reinterpret_cast<uint64_t*>(s_sf + 512);
+    uint8_t* s_codes_r = s_sf + 512;      // dual mode: [128 rows][64 B] + 512 B of scales
+    uint8_t* s_sf_r = s_codes_r + TT * 64;
+    uint64_t* bar = reinterpret_cast<uint64_t*>(DUAL ? s_sf_r + 512 : s_sf + 512);
 
     const int tid = threadIdx.x;
     const int col0 = blockIdx.x * TT;              // source column of the tile = output row
@@ -140,20 +149,45 @@ __global__ void __launch_bounds__(TT_THREADS, 4) quant_tile_t_kernel(const __gri
         s_sf[(oc & 31) * 16 + (oc >> 5) * 4 + rg] = (uint8_t)e8m0;
     }
 
+    if (DUAL && SRC != SRC_MXFP4) {
+        // row-wise pass over the same tile: thread -> (row, two of the row's four groups), as in quant_rows
+        const int warp = tid >> 5, lane = tid & 31;
+        const int row = (warp & 3) * 32 + lane;
+        const int64_t grow = (int64_t)row0 + row;
+#pragma unroll 1
+        for (int it = 0; it < 2; ++it) {
+            const int gk = (warp >> 2) * 2 + it;
+            float w[32];
+            load_row_group<SRC == SRC_F32>(s_in, row, gk, w);
+            wht32(w);
+            const uint64_t g = (uint64_t)grow * (uint64_t)(p.cols >> 5) + (uint64_t)((col0 >> 5) + gk);
+            const int64_t flat = grow * p.cols + col0 + gk * 32;
+            uint32_t words[4];
+            int e8m0;
+            absmax_quantize_group<ROUND>(w, p.had_scale, g, flat, true, p.seed_rows, p.offset, p.noise, flip, words, e8m0);
+            *reinterpret_cast<uint4*>(s_codes_r + row * 64 + gk * 16) = make_uint4(words[0], words[1], words[2], words[3]);
+            s_sf_r[(row & 31) * 16 + (row >> 5) * 4 + gk] = (uint8_t)e8m0;
+        }
+    }
+
     fence_proxy_async_smem();
     __syncthreads();
     if (tid == 0) {
         tma_store_2d(&tm_out, row0 / 2, col0, s_codes);
         uint8_t* sf_dst = p.sf_t + ((int64_t)blockIdx.x * p.sf_t_blocks_per_rowblock + blockIdx.y) * 512;
         bulk_store(sf_dst, s_sf, 512);
+        if (DUAL) {
+            tma_store_2d(&tm_rows, col0 / 2, row0, s_codes_r);
+            bulk_store(p.sf_rows + ((int64_t)blockIdx.y * p.sf_rows_blocks_per_rowblock + blockIdx.x) * 512, s_sf_r, 512);
+        }
         bulk_commit();
         bulk_wait_read0();
     }
 }
 
-template <int SRC, int ROUND>
-static int launch_tile_t(const void* src, const TileTParams& p, uint8_t* codes_t, cudaStream_t stream) {
-    CUtensorMap tm_in, tm_out;
+template <int SRC, int ROUND, bool DUAL = false>
+static int launch_tile_t(const void* src, const TileTParams& p, uint8_t* codes_t, cudaStream_t stream, uint8_t* codes_rows = nullptr) {
+    CUtensorMap tm_in, tm_out, tm_rows;
     int rc;
     if (SRC == SRC_F32)
         rc = make_tmap_2d(&tm_in, src, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, p.cols, p.rows, p.cols * 4, 32, TT, 3);
@@ -164,12 +198,14 @@ static int launch_tile_t(const void* src, const TileTParams& p, uint8_t* codes_t
     if (rc) return rc;
     rc = make_tmap_2d(&tm_out, codes_t, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, p.rows / 2, p.cols, p.rows / 2, 64, TT, 0);
     if (rc) return rc;
-    auto kern = quant_tile_t_kernel<SRC, ROUND>;
-    constexpr int smem = tile_smem_bytes<SRC>();
+    tm_rows = tm_out;
+    if (DUAL && (rc = make_tmap_2d(&tm_rows, codes_rows, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, p.cols / 2, p.rows, p.cols / 2, 64, TT, 0))) return rc;
+    auto kern = quant_tile_t_kernel<SRC, ROUND, DUAL>;
+    constexpr int smem = tile_smem_bytes<SRC, DUAL>();
     rc = check_cuda(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem), "cudaFuncSetAttribute");
     if (rc) return rc;
     dim3 grid((unsigned)(p.cols / TT), (unsigned)(p.rows / TT));
-    kern<<<grid, TT_THREADS, smem, stream>>>(tm_in, tm_out, p);
+    kern<<<grid, TT_THREADS, smem, stream>>>(tm_in, tm_out, tm_rows, p);
     return check_cuda(cudaGetLastError(), "quant_tile_t launch");
 }
 
@@ -240,4 +276,30 @@ extern "C" __attribute__((visibility("default"))) int quartet_requant_t(const ui
     p.had_scale = had_scale, p.signs = signs, p.signs_dev = signs_dev;
     p.seed = seed, p.offset = offset, p.noise = noise;
     return dispatch_round<SRC_MXFP4>(codes, p, codes_t, rounding, static_cast<cudaStream_t>(stream));
+}
+
+// Q(E) and Q(E^T) from one read of E: codes/sf are what quartet_quant_bwd(x, ..., seed_rows) writes,
+// codes_t/sf_t what quartet_quant_bwd_t(x, ..., seed_t) writes.
+extern "C" __attribute__((visibility("default"))) int quartet_quant_bwd_dual(const void* x, int x_dtype, int64_t rows, int64_t cols, float had_scale,
+                                      uint32_t signs, const uint32_t* signs_dev, int rounding, uint64_t seed_rows,
+                                      uint64_t seed_t, uint64_t offset, uint8_t* codes, uint8_t* sf, uint8_t* codes_t,
+                                      uint8_t* sf_t, quartet_stream_t stream) {
+    int rc = validate_tile_t(x, rows, cols, codes_t, sf_t, rounding, nullptr);
+    if (rc) return rc;
+    if (!codes || !sf) return fail(QUARTET_E_NULL, "codes and sf must be non-NULL");
+    if (!aligned16(codes) || !aligned16(sf)) return fail(QUARTET_E_ALIGN, "pointers must be 16-byte aligned");
+    if (x_dtype != QUARTET_BF16 && x_dtype != QUARTET_F32) return fail(QUARTET_E_ARG, "x_dtype must be 0 (bf16) or 1 (f32)");
+    if (rounding != QUARTET_ROUND_NEAREST && rounding != QUARTET_ROUND_SR_PHILOX)
+        return fail(QUARTET_E_ARG, "the dual quantizer supports rounding modes 0 and 1 (got %d)", rounding);
+    TileTParams p{};
+    p.rows = rows, p.cols = cols;
+    p.sf_t = sf_t, p.sf_t_blocks_per_rowblock = ((rows / 32 + 3) / 4);
+    p.sf_rows = sf, p.sf_rows_blocks_per_rowblock = ((cols / 32 + 3) / 4);
+    p.had_scale = had_scale, p.signs = signs, p.signs_dev = signs_dev;
+    p.seed = seed_t, p.seed_rows = seed_rows, p.offset = offset, p.noise = nullptr;
+    p.in_scale = 1.f;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (x_dtype == QUARTET_F32)
+        return rounding ? launch_tile_t<SRC_F32, 1, true>(x, p, codes_t, s, codes) : launch_tile_t<SRC_F32, 0, true>(x, p, codes_t, s, codes);
+    return rounding ? launch_tile_t<SRC_BF16, 1, true>(x, p, codes_t, s, codes) : launch_tile_t<SRC_BF16, 0, true>(x, p, codes_t, s, codes);
 }

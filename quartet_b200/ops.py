@@ -98,6 +98,24 @@ def quant_bwd_t(x, had_scale=HAD_SCALE_BF16, signs=0, signs_dev=None, rounding=R
     return codes_t, sf_t
 
 
+def quant_bwd_dual(x, had_scale=HAD_SCALE_BF16, signs=0, signs_dev=None, rounding=ROUND_SR_PHILOX, seed_rows=0, seed_t=0, offset=0):
+    """`quant_bwd(x, seed=seed_rows)` and `quant_bwd_t(x, seed=seed_t)` from one read of x:
+    (codes, sf, codes_t, sf_t), bit-identical to the two separate calls."""
+    _need_cuda(x, signs_dev)
+    rows, cols = x.shape
+    codes = torch.empty(rows, cols // 2, dtype=torch.uint8, device=x.device)
+    sf = torch.empty(sf_bytes(rows, cols), dtype=torch.uint8, device=x.device)
+    codes_t = torch.empty(cols, rows // 2, dtype=torch.uint8, device=x.device)
+    sf_t = torch.empty(sf_bytes(cols, rows), dtype=torch.uint8, device=x.device)
+    m64 = 2**64 - 1
+    with torch.cuda.device(x.device):
+        rc = _lib.load().quartet_quant_bwd_dual(_ptr(x), _dt(x), rows, cols, had_scale, int(signs) & 0xFFFFFFFF, _ptr(signs_dev), rounding,
+                                                int(seed_rows) & m64, int(seed_t) & m64, int(offset) & m64, _ptr(codes), _ptr(sf),
+                                                _ptr(codes_t), _ptr(sf_t), _stream())
+    _lib.check(rc, "quartet_quant_bwd_dual")
+    return codes, sf, codes_t, sf_t
+
+
 def requant_t(codes, sf, in_scale=1.0, had_scale=HAD_SCALE_BF16, signs=0, signs_dev=None, rounding=ROUND_SR_PHILOX, seed=0,
               offset=0, noise=None):
     """MXFP4 [rows, cols] -> backward-quantized transpose (codes_t [cols, rows/2], sf_t)."""

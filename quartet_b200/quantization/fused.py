@@ -68,13 +68,17 @@ class QuartetLinearFn(torch.autograd.Function):
         hb = g_q.had_scale
         alpha = (ops.SR_OPERAND_SCALE * g_q.out_scale) ** 2
         dx = dw = None
+        dual = None
+        if ctx.needs_input_grad[0] and ctx.needs_input_grad[1] and rounding in (ops.ROUND_NEAREST, ops.ROUND_SR_PHILOX):
+            # one read of E for both of its quantizations (same bits as the two separate calls below)
+            dual = ops.quant_bwd_dual(e2, hb, rounding=rounding, seed_rows=seeds[0], seed_t=seeds[2], **sg)
         if ctx.needs_input_grad[0]:
-            ec, es = ops.quant_bwd(e2, hb, rounding=rounding, seed=seeds[0], **sg)
+            ec, es = dual[:2] if dual is not None else ops.quant_bwd(e2, hb, rounding=rounding, seed=seeds[0], **sg)
             wtc, wts = ops.requant_t(wc, ws, 1.0, hb, rounding=rounding, seed=seeds[1], **sg)
             dx = ops.gemm_mxfp4_tn(ec, es, wtc, wts, alpha, mask=xm, had_scale=ctx.a_q.had_scale, out_dtype=ctx.x_dtype)
             dx = dx[:ctx.m_real].reshape(ctx.x_shape)
         if ctx.needs_input_grad[1]:
-            etc, ets = ops.quant_bwd_t(e2, hb, rounding=rounding, seed=seeds[2], **sg)
+            etc, ets = dual[2:] if dual is not None else ops.quant_bwd_t(e2, hb, rounding=rounding, seed=seeds[2], **sg)
             xtc, xts = ops.requant_t(xc, xs, 1.0, hb, rounding=rounding, seed=seeds[3], **sg)
             sink = ctx.wgrad_sink
             if sink is not None and sink.accepts(wc.shape[0], wc.shape[1] * 2, ctx.w_dtype):

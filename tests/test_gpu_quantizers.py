@@ -246,3 +246,21 @@ def test_roundtrip_property_large(ops):
     print("SR relative mean error", signed, "magnitude bias", mag)
     assert signed < 1e-4 and abs(mag) < 1e-4
     assert ops.device_status() == 0
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("rounding", [0, 1])
+def test_quant_bwd_dual_equals_the_two_separate_quantizers(ops, dtype, rounding):
+    """One read of E: the row-wise half is quant_bwd bit for bit, the transposed half quant_bwd_t bit for bit
+    (different seeds for the two, a non-trivial sign vector, a ragged number of tiles per SM)."""
+    g = torch.Generator().manual_seed(404)
+    x = (torch.randn(640, 384, generator=g) * 3e-3).to(dtype).cuda()
+    kw = dict(signs=0x9E3779B9, rounding=rounding)
+    c, s, ct, st = ops.quant_bwd_dual(x, ops.HAD_SCALE_BF16, seed_rows=11, seed_t=22, offset=5, **kw)
+    c1, s1 = ops.quant_bwd(x, ops.HAD_SCALE_BF16, seed=11, offset=5, **kw)
+    c2, s2 = ops.quant_bwd_t(x, ops.HAD_SCALE_BF16, seed=22, offset=5, **kw)
+    assert torch.equal(c, c1) and torch.equal(s, s1)
+    assert torch.equal(ct, c2) and torch.equal(st, s2)
+    with pytest.raises(ValueError):
+        ops.quant_bwd_dual(x[:100], ops.HAD_SCALE_BF16)  # rows not a multiple of 128
+    assert ops.device_status() == 0
