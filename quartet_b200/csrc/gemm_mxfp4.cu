@@ -451,7 +451,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_mxfp4_kernel(const __gri
 // the whole tile into its own tensor memory.  Cross-CTA signalling uses remote mbarrier arrives
 // and tcgen05.commit onto the peer's barriers; no multicast copy is involved.
 // ===========================================================================================
-template <int BN>
+template <int BN, int NSTG = 1>
 struct Gemm2Cfg {
     static constexpr int NSEG = BN / 32;                     // 32-row segments of B = scale columns per K-chunk
     static constexpr int SFB_ST = NSEG <= 4 ? 4 : 8;         // columns written per tcgen05.st
@@ -472,7 +472,7 @@ struct Gemm2Cfg {
     static constexpr int SFB_BLOCKS = (BN % 128 == 0) ? BN / 128 : BN / 128 + 2;  // 128-row scale blocks a tile can touch
     static constexpr int SFB_BYTES = SFB_BLOCKS * 1024;
     static constexpr int STAGE_BYTES = A_BYTES + B_BYTES + SFA_BYTES + SFB_BYTES;
-    static constexpr int STG_BYTES = 8 * 2048;               // epilogue staging: 2 KB per epilogue warp (8 warps)
+    static constexpr int STG_BYTES = 8 * NSTG * 2048;        // epilogue staging: NSTG buffers of 2 KB per epilogue warp (8 warps)
     static constexpr int STAGES = (232448 - STG_BYTES - 256) / STAGE_BYTES;
     static constexpr int SMEM = STAGES * STAGE_BYTES + STG_BYTES + 256;
     static_assert(SF_COL0 + SF_SLOTS * SF_COLS <= TMEM_COLS, "tensor memory budget");
@@ -566,12 +566,12 @@ __device__ __forceinline__ void tile_coords(int tile, int m_pairs, int n_tiles, 
     m_pair = band * RASTER_BAND + (within - n_blk * rows);
 }
 
-template <int BN>
+template <int BN, int NSTG>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM2_THREADS, 1)
     gemm_mxfp4_2cta_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                            const __grid_constant__ CUtensorMap tm_d, const __grid_constant__ ScatterMaps sc,
                            const GemmParams p) {
-    using C = Gemm2Cfg<BN>;
+    using C = Gemm2Cfg<BN, NSTG>;
     // Dynamic shared memory is the kernel's only shared memory and starts 1024-byte aligned (checked
     // below); no slack is reserved for re-aligning it, which is what makes room for a sixth stage.
     extern __shared__ __align__(1024) uint8_t smem_raw[];
@@ -795,7 +795,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM2_THREADS, 1)
         // warps 11-14 the odd ones; the next block's tcgen05.ld is in flight while one is processed.
         const int q = warp & 3;
         const int par = warp >= 11 ? 1 : 0;
-        uint8_t* stg = s_stg + (par * 4 + q) * 2048;
+        uint8_t* stg = s_stg + (par * 4 + q) * (NSTG * 2048);
         uint32_t acc_it = 0, n_stores = 0;
         for (int tile = cluster_id; tile < n_tiles_total && !*dead; tile += n_clusters, ++acc_it) {
             int m_pair, n_blk;
@@ -828,13 +828,13 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM2_THREADS, 1)
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive_cluster(mapa_u32(smem_u32(&acc_empty[0]), 0));
-                if (c0 < n_chunks) epilogue_block<1>(ra, p, tmd, row, row0, n0 + c0 * 32, stg, n_stores, lane);
+                if (c0 < n_chunks) epilogue_block<NSTG>(ra, p, tmd, row, row0, n0 + c0 * 32, stg, n_stores, lane);
                 if (c2 < n_chunks) tc_ld32(t0 + c2 * 32, ra);
-                if (c1 < n_chunks) epilogue_block<1>(rb, p, tmd, row, row0, n0 + c1 * 32, stg, n_stores, lane);
+                if (c1 < n_chunks) epilogue_block<NSTG>(rb, p, tmd, row, row0, n0 + c1 * 32, stg, n_stores, lane);
                 if (c3 < n_chunks) tc_ld32(t0 + c3 * 32, rb);
                 tc_wait_ld();
-                if (c2 < n_chunks) epilogue_block<1>(ra, p, tmd, row, row0, n0 + c2 * 32, stg, n_stores, lane);
-                if (c3 < n_chunks) epilogue_block<1>(rb, p, tmd, row, row0, n0 + c3 * 32, stg, n_stores, lane);
+                if (c2 < n_chunks) epilogue_block<NSTG>(ra, p, tmd, row, row0, n0 + c2 * 32, stg, n_stores, lane);
+                if (c3 < n_chunks) epilogue_block<NSTG>(rb, p, tmd, row, row0, n0 + c3 * 32, stg, n_stores, lane);
                 // all of this tile's tensor-memory reads are complete before the warp's next arrive
                 tc_fence_before();
             } else {
@@ -843,11 +843,11 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM2_THREADS, 1)
                 for (int ch = par; ch < n_chunks; ch += 4) {
                     tc_wait_ld();
                     if (ch + 2 < n_chunks) tc_ld32(t0 + (ch + 2) * 32, rb);
-                    epilogue_block<1>(ra, p, tmd, row, row0, n0 + ch * 32, stg, n_stores, lane);
+                    epilogue_block<NSTG>(ra, p, tmd, row, row0, n0 + ch * 32, stg, n_stores, lane);
                     if (ch + 2 < n_chunks) {
                         tc_wait_ld();
                         if (ch + 4 < n_chunks) tc_ld32(t0 + (ch + 4) * 32, ra);
-                        epilogue_block<1>(rb, p, tmd, row, row0, n0 + (ch + 2) * 32, stg, n_stores, lane);
+                        epilogue_block<NSTG>(rb, p, tmd, row, row0, n0 + (ch + 2) * 32, stg, n_stores, lane);
                     }
                 }
                 tc_fence_before();
@@ -873,10 +873,10 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM2_THREADS, 1)
     }
 }
 
-template <int BN>
+template <int BN, int NSTG = 1>
 static int launch_gemm_2cta(const uint8_t* a, const uint8_t* b, void* d, const GemmParams& p0, cudaStream_t stream,
                             void* const* owners = nullptr, int n_owners = 0) {
-    using C = Gemm2Cfg<BN>;
+    using C = Gemm2Cfg<BN, NSTG>;
     GemmParams p = p0;
     p.n_tiles = (p.N + BN - 1) / BN;
     CUtensorMap tm_a, tm_b, tm_d;
@@ -900,7 +900,7 @@ static int launch_gemm_2cta(const uint8_t* a, const uint8_t* b, void* d, const G
     else
         rc = make_tmap_2d(&tm_d, d, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, p.N, p.M, (uint64_t)p.N * 2, 32, 32, 2);
     if (rc) return rc;
-    auto kern = gemm_mxfp4_2cta_kernel<BN>;
+    auto kern = gemm_mxfp4_2cta_kernel<BN, NSTG>;
     rc = check_cuda(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM), "cudaFuncSetAttribute");
     if (rc) return rc;
     int dev = 0, sms = 0;
@@ -1061,5 +1061,7 @@ extern "C" __attribute__((visibility("default"))) int quartet_gemm_mxfp4_tn_scat
     p.alpha = alpha, p.mask = mask, p.had_scale = had_scale;
     p.d_f32 = 1;
     p.rows_per_owner = (int)rows_per_owner;
-    return launch_gemm_2cta<256>(a, b, nullptr, p, static_cast<cudaStream_t>(stream), owners, n_owners);
+    // two staging buffers per epilogue warp (and five operand stages instead of six): a store to a peer
+    // holds its staging buffer longer than a local one
+    return launch_gemm_2cta<256, 2>(a, b, nullptr, p, static_cast<cudaStream_t>(stream), owners, n_owners);
 }
