@@ -2,8 +2,8 @@
 
 TEST INFRASTRUCTURE ONLY (used by tests/golden/make_golden.py and by CPU tests
 that are skipped when the reference tree is absent).  No reference source is
-copied: the modules are imported from where they lie (env QUARTET_REF, default
-/root/reference/src) after three shims:
+copied: the modules are imported from where they lie (the `src` directory of a
+reference checkout, named by the environment variable QUARTET_REF) after three shims:
 
 1. TRITON_INTERPRET=1 so `mxfp4_forward_kernel` (mxfp4_triton.py:19-174) runs
    under Triton's numpy interpreter, and TORCHDYNAMO_DISABLE=1 so the

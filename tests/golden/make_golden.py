@@ -2,7 +2,7 @@
 
 Run from the repo root in a container that has the reference tree:
 
-    python tests/golden/make_golden.py            # QUARTET_REF=/root/reference/src
+    QUARTET_REF=<reference checkout>/src python tests/golden/make_golden.py
 
 The reference kernel (src/models/quantization/quantizers/mxfp4_triton.py) is
 executed under the Triton interpreter through oracle/ref_import.py; the
