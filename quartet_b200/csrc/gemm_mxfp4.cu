@@ -41,7 +41,7 @@ __device__ long long g_trace[16][64];
 constexpr int BM = 128;
 constexpr int BK_BYTES = 128;   // 256 e2m1 elements per stage along K
 constexpr int GEMM_THREADS = 320;  // warp 0 TMA, warp 1 MMA, warps 2-5 epilogue, warps 6-9 scale feeders
-constexpr int GEMM2_THREADS = 480; // two-CTA kernel: warp 10 issues the scale copies, warps 11-14 are four more epilogue warps
+constexpr int GEMM2_THREADS = 512; // two-CTA kernel: warps 0, 10, 15 issue copies (A, B, scales), 11-14 are four more epilogue warps
 
 template <int BN>
 struct GemmCfg {
@@ -217,7 +217,7 @@ __device__ __forceinline__ void epilogue_block(const uint32_t (&r)[32], const Ge
             fence_proxy_async_smem();
             __syncwarp();
             if (lane == 0) {
-                tma_store_2d(tm_d, col, row0 + 16 * hf, buf);
+                tma_store_2d_hint(tm_d, col, row0 + 16 * hf, buf, l2_policy_evict_first());
                 bulk_commit();
             }
         }
@@ -240,7 +240,7 @@ __device__ __forceinline__ void epilogue_block(const uint32_t (&r)[32], const Ge
         fence_proxy_async_smem();
         __syncwarp();
         if (lane == 0) {
-            tma_store_2d(tm_d, col, row0, buf);
+            tma_store_2d_hint(tm_d, col, row0, buf, l2_policy_evict_first());
             bulk_commit();
         }
     }
@@ -569,8 +569,8 @@ __device__ __forceinline__ void tile_coords(int tile, int m_pairs, int n_tiles, 
 template <int BN, int NSTG>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM2_THREADS, 1)
     gemm_mxfp4_2cta_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
-                           const __grid_constant__ CUtensorMap tm_d, const __grid_constant__ ScatterMaps sc,
-                           const GemmParams p) {
+                           const __grid_constant__ CUtensorMap tm_d, const __grid_constant__ CUtensorMap tm_sfb,
+                           const __grid_constant__ ScatterMaps sc, const GemmParams p) {
     using C = Gemm2Cfg<BN, NSTG>;
     // Dynamic shared memory is the kernel's only shared memory and starts 1024-byte aligned (checked
     // below); no slack is reserved for re-aligning it, which is what makes room for a sixth stage.
@@ -600,7 +600,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM2_THREADS, 1)
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < C::STAGES; ++i) {
-            mbar_init(&full[i], 2);  // operand producer + scale producer
+            mbar_init(&full[i], 3);  // the A, B and scale producers
             mbar_init(&empty[i], 1);
             mbar_init(&sf_full[i], 8);
         }
@@ -631,13 +631,15 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM2_THREADS, 1)
     const int k_stages = (p.k_chunks + 1) >> 1;
     const int64_t sf_blocks_per_rowblock = p.k_chunks;
 
-    if (warp == 0 || warp == 10) {
+    if (warp == 0 || warp == 10 || warp == 15) {
         // ------------------------------ TMA producers (both CTAs) ------------------------------
-        // warp 0 issues the two operand tensor copies of a stage, warp 10 the stage's scale blocks;
-        // both count on the stage's one `full` barrier.  (One thread issuing all five copies of a stage
-        // could not keep up with the tensor pipe.)
+        // Three threads in three warps, each counting on the stage's one `full` barrier: warp 0 copies this
+        // CTA's rows of A, warp 10 its half of B, warp 15 the scales (one bulk copy for A's, one tensor copy
+        // for all row blocks of B's).  Issuing a bulk/tensor copy occupies the issuing thread for a few
+        // hundred cycles, so one thread cannot start a stage's copies in the 520 cycles its MMAs take.
         if (lane == 0) {
-            const bool ops_role = warp == 0;
+            const int role = warp == 0 ? 0 : (warp == 10 ? 1 : 2);
+            const uint64_t keep = l2_policy_evict_last();  // operands and scales are re-read by other CTAs
             uint32_t s = 0, ph = 0;
             [[maybe_unused]] uint32_t tr = 0;
             for (int tile = cluster_id; tile < n_tiles_total && !*dead; tile += n_clusters) {
@@ -645,26 +647,24 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM2_THREADS, 1)
                 tile_coords(tile, m_pairs, p.n_tiles, m_pair, n_blk);
                 const int m_blk = m_pair * 2 + (int)rank;
                 const int m0 = m_blk * BM, n0 = n_blk * BN;
-                const int blk0 = n0 / 128;
-                const int n_blocks = (min(n0 + BN, p.N) - 1) / 128 - blk0 + 1;
                 const uint8_t* sfa_src = p.a_sf + (int64_t)m_blk * sf_blocks_per_rowblock * 512;
-                const uint8_t* sfb_src = p.b_sf + (int64_t)blk0 * sf_blocks_per_rowblock * 512;
                 for (int ks = 0; ks < k_stages; ++ks) {
-                    if (ops_role) TRACE(13, tr);
+                    if (role == 0) TRACE(13, tr);
                     if (!gemm_wait(&empty[s], ph ^ 1, WAIT_GEMM_EMPTY, dead)) break;
-                    if (ops_role) {
+                    if (role == 0) {
                         TRACE(0, tr);
                         ++tr;
-                        mbar_arrive_expect_tx(&full[s], C::A_BYTES + C::B_BYTES);
-                        tma_load_2d(s_a + s * C::A_BYTES, &tm_a, ks * BK_BYTES, m0, &full[s]);
-                        tma_load_2d(s_b + s * C::B_BYTES, &tm_b, ks * BK_BYTES, n0 + (int)rank * (BN / 2), &full[s]);
+                        mbar_arrive_expect_tx(&full[s], C::A_BYTES);
+                        tma_load_2d_hint(s_a + s * C::A_BYTES, &tm_a, ks * BK_BYTES, m0, &full[s], keep);
+                    } else if (role == 1) {
+                        mbar_arrive_expect_tx(&full[s], C::B_BYTES);
+                        tma_load_2d_hint(s_b + s * C::B_BYTES, &tm_b, ks * BK_BYTES, n0 + (int)rank * (BN / 2), &full[s], keep);
                     } else {
+                        // the tensor copy always delivers its full box (out-of-range parts are zero-filled)
                         const int nch = min(2, p.k_chunks - 2 * ks);
-                        mbar_arrive_expect_tx(&full[s], nch * 512 * (1 + n_blocks));
-                        bulk_load(s_sfa + s * C::SFA_BYTES, sfa_src + (int64_t)ks * 1024, nch * 512, &full[s]);
-                        for (int rb = 0; rb < n_blocks; ++rb)
-                            bulk_load(s_sfb + s * C::SFB_BYTES + rb * 1024,
-                                      sfb_src + ((int64_t)rb * sf_blocks_per_rowblock + 2 * ks) * 512, nch * 512, &full[s]);
+                        mbar_arrive_expect_tx(&full[s], nch * 512 + C::SFB_BYTES);
+                        bulk_load_hint(s_sfa + s * C::SFA_BYTES, sfa_src + (int64_t)ks * 1024, nch * 512, &full[s], keep);
+                        tma_load_2d_hint(s_sfb + s * C::SFB_BYTES, &tm_sfb, ks * 256, n0 / 128, &full[s], keep);
                     }
                     if (++s == C::STAGES) s = 0, ph ^= 1;
                 }
@@ -900,6 +900,13 @@ static int launch_gemm_2cta(const uint8_t* a, const uint8_t* b, void* d, const G
     else
         rc = make_tmap_2d(&tm_d, d, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, p.N, p.M, (uint64_t)p.N * 2, 32, 32, 2);
     if (rc) return rc;
+    // B's scales as a 2-D tensor of 32-bit words: one row per 128-row block, k_chunks * 128 words each;
+    // a stage takes two chunks (256 words) of every row block of the tile in one copy
+    CUtensorMap tm_sfb;
+    static_assert(BN % 128 == 0, "the scale copy of the two-CTA kernel assumes tiles that start on a 128-row scale block");
+    if ((rc = make_tmap_2d(&tm_sfb, p.b_sf, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, (uint64_t)p.k_chunks * 128, (uint64_t)((p.N + 127) / 128),
+                           (uint64_t)p.k_chunks * 512, 256, BN / 128, 0)))
+        return rc;
     auto kern = gemm_mxfp4_2cta_kernel<BN, NSTG>;
     rc = check_cuda(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM), "cudaFuncSetAttribute");
     if (rc) return rc;
@@ -929,7 +936,7 @@ static int launch_gemm_2cta(const uint8_t* a, const uint8_t* b, void* d, const G
 #ifdef QUARTET_GEMM_TRACE
     if (const char* e = getenv("QUARTET_GEMM_MAX_CLUSTERS")) clusters = clusters < atoi(e) ? clusters : atoi(e);
 #endif
-    kern<<<clusters * 2, GEMM2_THREADS, C::SMEM, stream>>>(tm_a, tm_b, tm_d, *scp, p);
+    kern<<<clusters * 2, GEMM2_THREADS, C::SMEM, stream>>>(tm_a, tm_b, tm_d, tm_sfb, *scp, p);
 #ifdef QUARTET_GEMM_TRACE
     {
         static long long h[16][64];
@@ -1009,7 +1016,7 @@ extern "C" __attribute__((visibility("default"))) int quartet_gemm_mxfp4_tn(cons
     p.alpha = alpha, p.mask = mask, p.had_scale = had_scale;
     p.d_f32 = d_dtype == QUARTET_F32;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    // Tile width: 256 unless the output is narrow or not a multiple of 256.  QUARTET_GEMM_BN=128|224|256
+    // Tile width: 256 unless the output is narrow or not a multiple of 256.  QUARTET_GEMM_BN=128|256
     // overrides the choice (tuning aid).
     static const int forced_bn = [] {
         const char* e = getenv("QUARTET_GEMM_BN");
@@ -1019,13 +1026,10 @@ extern "C" __attribute__((visibility("default"))) int quartet_gemm_mxfp4_tn(cons
         const char* e = getenv("QUARTET_GEMM_CTAS");
         return e ? atoi(e) : 0;
     }();
-    const bool wide = forced_bn ? forced_bn >= 224 : (N % 256 == 0 || N > 1024);
+    const bool wide = forced_bn ? forced_bn >= 256 : (N % 256 == 0 || N > 1024);
     // CTA pairs need an even number of 128-row tiles; QUARTET_GEMM_CTAS=1|2 overrides (tuning aid).
     const bool pair = forced_cta ? forced_cta == 2 : true;
     if (pair && wide && M % 256 == 0) {
-        // 256-wide tiles with one accumulator measure faster than 224-wide double-buffered ones
-        // (the latter leave room for only two scale slots in tensor memory, which throttles the feeders)
-        if (forced_bn == 224) return launch_gemm_2cta<224>(a, b, d, p, s);
         return launch_gemm_2cta<256>(a, b, d, p, s);
     }
     if (wide) return launch_gemm<256>(a, b, d, p, s);
