@@ -169,6 +169,15 @@ int quartet_peer_close(void* ptr);
 /* Asynchronous device-to-device copy (DMA engines, no SM): e.g. local partial rows -> a slot of a peer's buffer. */
 int quartet_peer_copy(void* dst, const void* src, uint64_t bytes, quartet_stream_t stream);
 
+/*
+ * Measurement aid (no reference counterpart): bytes per clock one SM takes in through bulk asynchronous
+ * copies from `src` (`region` bytes, keep it L2-resident), with `producers` (1..4) issuing threads per SM,
+ * each running a ring of `stages` buffers of `chunk` bytes for `iters` copies.  `cycles` is a device
+ * array of one int64 per SM; the call synchronises the stream and writes the result to the host.
+ */
+int quartet_probe_copy_ingress(const void* src, uint64_t region, int32_t iters, int32_t stages, int32_t chunk,
+                               int32_t producers, int64_t* cycles, double* bytes_per_clk_per_sm, quartet_stream_t stream);
+
 /* Host helpers for the blocked scale layout (`to_blocked`, benchmark_mxfp4.ipynb:1015-1016). */
 int64_t quartet_sf_offset(int64_t row, int64_t kblock, int64_t padded_kblocks);
 int64_t quartet_sf_bytes(int64_t rows, int64_t cols);

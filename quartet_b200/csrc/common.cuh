@@ -29,6 +29,7 @@ int status_rows(int32_t* out);
 int status_tile_t(int32_t* out);
 int status_gemm(int32_t* out);
 int status_aux(int32_t* out);
+int status_probe(int32_t* out);
 
 static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 

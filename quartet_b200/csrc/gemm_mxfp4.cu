@@ -635,8 +635,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM2_THREADS, 1)
         // ------------------------------ TMA producers (both CTAs) ------------------------------
         // Three threads in three warps, each counting on the stage's one `full` barrier: warp 0 copies this
         // CTA's rows of A, warp 10 its half of B, warp 15 the scales (one bulk copy for A's, one tensor copy
-        // for all row blocks of B's).  Issuing a bulk/tensor copy occupies the issuing thread for a few
-        // hundred cycles, so one thread cannot start a stage's copies in the 520 cycles its MMAs take.
+        // for all row blocks of B's).  A thread can start a copy only every few hundred cycles, and a
+        // stage's MMAs take 520: with one or two issuing threads the copies of a stage started too late.
         if (lane == 0) {
             const int role = warp == 0 ? 0 : (warp == 10 ? 1 : 2);
             const uint64_t keep = l2_policy_evict_last();  // operands and scales are re-read by other CTAs

@@ -1,0 +1,97 @@
+// Measurement aid: how many bytes per clock ONE SM can take in through bulk asynchronous copies
+// (the mechanism that feeds the GEMM's operand ring), as a function of how many threads issue the
+// copies, how large a copy is and how many are in flight.  One CTA per SM; `producers` threads in
+// different warps each run their own ring of `stages` buffers over an L2-resident source region;
+// a partner thread per producer releases a buffer as soon as it has landed.  Nothing is computed.
+//
+// Findings on B200 that shaped the GEMM: one issuing thread moves ~62 B/clk with 16 KB copies (it can
+// start a copy about every 265 cycles); two or more issuing warps saturate the SM's ingress at
+// ~70 B/clk, whatever the copy size above 8 KB; the unloaded issue -> landed -> released round trip of
+// a 16 KB copy from L2 is ~645 cycles.  Full-rate MXFP4 MMAs on 256 x 256 tiles need 67 B/clk.
+#include "common.cuh"
+
+namespace quartet {
+
+constexpr int PROBE_THREADS = 256;
+constexpr int PROBE_MAX_PRODUCERS = 4;
+
+__global__ void __launch_bounds__(PROBE_THREADS, 1)
+    probe_ingress_kernel(const uint8_t* __restrict__ src, uint64_t region, int iters, int stages, uint32_t chunk, int producers,
+                         long long* __restrict__ cycles) {
+    extern __shared__ __align__(1024) uint8_t smem[];
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + (size_t)producers * stages * chunk);
+    const int w = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < 2 * producers * stages; ++i) mbar_init(&bars[i], 1);
+        fence_mbar_init();
+    }
+    __syncthreads();
+    const long long t0 = clock64();
+    if (lane == 0 && w < producers) {
+        uint64_t* full = bars + w * 2 * stages;
+        uint64_t* empty = full + stages;
+        uint8_t* buf = smem + (size_t)w * stages * chunk;
+        uint64_t off = ((((uint64_t)blockIdx.x * 7919u + (uint64_t)w * 104729u) * chunk) % (region - chunk)) & ~uint64_t(127);
+        int s = 0;
+        uint32_t ph = 0;
+        for (int k = 0; k < iters; ++k) {
+            if (!mbar_wait(&empty[s], ph ^ 1, WAIT_QUANT_LOAD)) break;
+            mbar_arrive_expect_tx(&full[s], chunk);
+            bulk_load(buf + (size_t)s * chunk, src + off, chunk, &full[s]);
+            off += (uint64_t)chunk * 149u;
+            if (off + chunk > region) off -= region - chunk;
+            if (++s == stages) s = 0, ph ^= 1;
+        }
+    } else if (lane == 0 && w >= PROBE_MAX_PRODUCERS && w < PROBE_MAX_PRODUCERS + producers) {
+        uint64_t* full = bars + (w - PROBE_MAX_PRODUCERS) * 2 * stages;
+        uint64_t* empty = full + stages;
+        int s = 0;
+        uint32_t ph = 0;
+        for (int k = 0; k < iters; ++k) {
+            if (!mbar_wait(&full[s], ph, WAIT_QUANT_LOAD)) break;
+            mbar_arrive(&empty[s]);
+            if (++s == stages) s = 0, ph ^= 1;
+        }
+        if (w == PROBE_MAX_PRODUCERS) cycles[blockIdx.x] = clock64() - t0;
+    }
+}
+
+QUARTET_DEFINE_STATUS_READER(status_probe)
+
+}  // namespace quartet
+
+using namespace quartet;
+
+// bytes_per_clk_per_sm = iters * chunk * producers / (slowest CTA's cycles).  `src` is a device buffer of
+// `region` bytes (keep it below the L2 size to measure the L2 -> SM path), `cycles` a device array of
+// one int64 per SM used as scratch for the result.
+extern "C" __attribute__((visibility("default"))) int quartet_probe_copy_ingress(const void* src, uint64_t region, int32_t iters, int32_t stages,
+                                                                                 int32_t chunk, int32_t producers, int64_t* cycles,
+                                                                                 double* bytes_per_clk_per_sm, quartet_stream_t stream) {
+    if (!src || !cycles || !bytes_per_clk_per_sm) return fail(QUARTET_E_NULL, "src, cycles and the result pointer must be non-NULL");
+    if (producers < 1 || producers > PROBE_MAX_PRODUCERS || stages < 1 || stages > 32 || iters < 1)
+        return fail(QUARTET_E_ARG, "need 1..%d producers, 1..32 stages, iters >= 1", PROBE_MAX_PRODUCERS);
+    if (chunk < 128 || chunk % 128 || region < 4ull * chunk || !aligned16(src))
+        return fail(QUARTET_E_ARG, "chunk must be a positive multiple of 128 bytes, region >= 4 chunks, src 16-byte aligned");
+    const size_t smem = (size_t)producers * stages * chunk + 2 * (size_t)producers * stages * 8 + 64;
+    if (smem > 220 * 1024) return fail(QUARTET_E_ARG, "producers * stages * chunk exceeds the shared memory of an SM");
+    int rc = bind_context_of(src);
+    if (rc) return rc;
+    if ((rc = check_device())) return rc;
+    int sms = 0;
+    if ((rc = device_sm_count(&sms))) return rc;
+    if ((rc = check_cuda(cudaFuncSetAttribute(probe_ingress_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem), "cudaFuncSetAttribute")))
+        return rc;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    probe_ingress_kernel<<<sms, PROBE_THREADS, smem, s>>>(static_cast<const uint8_t*>(src), region, iters, stages, (uint32_t)chunk, producers,
+                                                          reinterpret_cast<long long*>(cycles));
+    if ((rc = check_cuda(cudaGetLastError(), "probe launch"))) return rc;
+    if ((rc = check_cuda(cudaStreamSynchronize(s), "probe run"))) return rc;
+    static long long host[1024];
+    if (sms > 1024) return fail(QUARTET_E_ARG, "more SMs than the probe's host buffer holds");
+    if ((rc = check_cuda(cudaMemcpy(host, cycles, sizeof(long long) * sms, cudaMemcpyDeviceToHost), "probe read-back"))) return rc;
+    long long worst = 1;
+    for (int i = 0; i < sms; ++i) worst = host[i] > worst ? host[i] : worst;
+    *bytes_per_clk_per_sm = (double)iters * chunk * producers / (double)worst;
+    return QUARTET_OK;
+}

@@ -112,7 +112,7 @@ def run_gemm(m, n, k, iters, warmup, fused, out_f32):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--kernel", default="quant_fwd", choices=["quant_fwd", "quant_bwd", "quant_bwd_t", "requant_t", "gemm"])
+    ap.add_argument("--kernel", default="quant_fwd", choices=["quant_fwd", "quant_bwd", "quant_bwd_t", "requant_t", "gemm", "copy_ingress"])
     ap.add_argument("--rows", type=int, default=16384)
     ap.add_argument("--cols", type=int, default=4096)
     ap.add_argument("--m", type=int, default=16384)
@@ -136,6 +136,13 @@ def main():
                     for kern in ("quant_fwd", "quant_bwd", "quant_bwd_t"):
                         print(json.dumps(run_quant(kern, m, k, torch.bfloat16, args.rounding, 5, 2, False)), flush=True)
                 m *= 2
+        return
+    if args.kernel == "copy_ingress":
+        # what one SM can take in through bulk copies: issuing threads x ring depth x copy size
+        for producers, stages, chunk in ((1, 1, 16384), (1, 6, 16384), (2, 6, 16384), (4, 3, 16384), (2, 3, 32768), (4, 6, 8192)):
+            v = ops.probe_copy_ingress(producers=producers, stages=stages, chunk=chunk)
+            print(json.dumps({"kernel": "copy_ingress", "producers": producers, "stages": stages, "chunk": chunk,
+                              "bytes_per_clk_per_sm": round(v, 1)}), flush=True)
         return
     if args.kernel == "gemm":
         print(json.dumps(run_gemm(args.m, args.n, args.k, args.iters, args.warmup, args.fused_unrotate, args.out_f32)))

@@ -212,6 +212,19 @@ def peer_free(ptr, device):
         _lib.check(_lib.load().quartet_peer_free(int(ptr)), "quartet_peer_free")
 
 
+def probe_copy_ingress(region_mb=48, iters=4000, stages=6, chunk=16384, producers=2, device="cuda"):
+    """Bytes per clock one SM takes in through bulk asynchronous copies (see csrc/probe_ingress.cu)."""
+    import ctypes as C
+
+    src = torch.ones(region_mb << 20, dtype=torch.uint8, device=device)
+    cycles = torch.zeros(1024, dtype=torch.int64, device=device)
+    out = C.c_double(0.0)
+    with torch.cuda.device(src.device):
+        rc = _lib.load().quartet_probe_copy_ingress(_ptr(src), src.numel(), iters, stages, chunk, producers, _ptr(cycles), C.byref(out), _stream())
+    _lib.check(rc, "quartet_probe_copy_ingress")
+    return out.value
+
+
 def unrotate_mask(g, mask=None, had_scale=HAD_SCALE_BF16, out_dtype=None):
     """((g * mask).view(-1, 32) @ H^T).view_as(g)"""
     _need_cuda(g, mask)
