@@ -37,7 +37,7 @@ METRIC = "quantized_linear_fwd_bwd_tflops"
 # DRAM traffic of the GEMM, from the ncu capture summarised in profiles/gemm_mxfp4_2cta_8192x8192x4096.md
 # (dram__bytes_read.sum + dram__bytes_write.sum of one launch).  The bench's launches are larger than the
 # capture rule allows, so the captured traffic is scaled by algorithmic bytes (operands + scales + result).
-NCU_GEMM_CAPTURE = {"m": 8192, "n": 8192, "k": 4096, "out_bytes": 2, "dram_bytes": 39.87e6 + 90.74e6}
+NCU_GEMM_CAPTURE = {"m": 8192, "n": 8192, "k": 4096, "out_bytes": 2, "dram_bytes": 36.13e6 + 84.27e6}
 
 
 def gemm_algorithmic_bytes(m, n, k, out_bytes):
@@ -342,7 +342,7 @@ def gpu_arm(args):
         "clocks": clocks,
         "roofline": {"bound": "tensor", "kernel": "gemm_mxfp4_2cta_kernel", "achieved": round(gemm_tflops, 1), "peak": round(4 * bf16_peak, 1),
                      "unit": "TFLOP/s", "frac": round(gemm_tflops / (4 * bf16_peak), 4), "traffic": round(gemm_traffic_per_launch(TOKENS)[0]),
-                     "traffic_note": "DRAM bytes per launch: ncu capture of 8192x8192x4096 (130.6 MB) scaled by algorithmic bytes to the step's average launch (%d MB algorithmic)" % round(gemm_traffic_per_launch(TOKENS)[1] / 1e6),
+                     "traffic_note": "DRAM bytes per launch: ncu capture of 8192x8192x4096 (120.4 MB) scaled by algorithmic bytes to the step's average launch (%d MB algorithmic)" % round(gemm_traffic_per_launch(TOKENS)[1] / 1e6),
                      "peak_note": f"4 x {peak_note} sustained bf16 cuBLAS rate (MXFP4:bf16 dense ratio of the tensor cores)",
                      "launches": g["n"], "avg_ms": round(g["ms"] / g["n"], 4)},
         "roofline_quantizers": {"bound": "hbm", "achieved": round(q_gbs, 1), "peak": hbm_peak, "unit": "GB/s", "frac": round(q_gbs / hbm_peak, 4),

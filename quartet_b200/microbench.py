@@ -22,7 +22,8 @@ import torch
 
 from . import ops
 
-BYTES_PER_ELEM = {"quant_fwd": 0.5 + 1 / 32 + 1 / 8, "quant_bwd": 0.5 + 1 / 32, "quant_bwd_t": 0.5 + 1 / 32}
+BYTES_PER_ELEM = {"quant_fwd": 0.5 + 1 / 32 + 1 / 8, "quant_bwd": 0.5 + 1 / 32, "quant_bwd_t": 0.5 + 1 / 32,
+                  "quant_bwd_dual": 2 * (0.5 + 1 / 32)}
 
 
 def _peaks():
@@ -81,6 +82,8 @@ def run_quant(kernel, rows, cols, dtype, rounding, iters, warmup, gauss):
             fn = lambda: ops.quant_fwd(x, ops.HAD_SCALE_BF16 if esz == 2 else ops.HAD_SCALE_F32)  # noqa: E731
         elif kernel == "quant_bwd":
             fn = lambda: ops.quant_bwd(x, rounding=rounding, seed=1)  # noqa: E731
+        elif kernel == "quant_bwd_dual":
+            fn = lambda: ops.quant_bwd_dual(x, rounding=rounding, seed_rows=1, seed_t=2)  # noqa: E731
         else:
             fn = lambda: ops.quant_bwd_t(x, rounding=rounding, seed=1)  # noqa: E731
         bytes_ = rows * cols * (esz + BYTES_PER_ELEM[kernel])
@@ -112,7 +115,7 @@ def run_gemm(m, n, k, iters, warmup, fused, out_f32):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--kernel", default="quant_fwd", choices=["quant_fwd", "quant_bwd", "quant_bwd_t", "requant_t", "gemm", "copy_ingress"])
+    ap.add_argument("--kernel", default="quant_fwd", choices=["quant_fwd", "quant_bwd", "quant_bwd_t", "quant_bwd_dual", "requant_t", "gemm", "copy_ingress"])
     ap.add_argument("--rows", type=int, default=16384)
     ap.add_argument("--cols", type=int, default=4096)
     ap.add_argument("--m", type=int, default=16384)
