@@ -186,6 +186,10 @@ def gpu_arm(args):
     # wgrad exchange across ranks: rows of each partial dW go straight from the GEMM epilogue into their
     # owner's memory ("peer", the default), or a NCCL reduce-scatter of full partials ("nccl")
     reducer = sink = None
+    if args.exchange == "auto":
+        # measured: with half of the rows remote the GEMM's own stores win; from 4 ranks on they slow the GEMM more
+        # than the DMA engines cost
+        args.exchange = "peer" if world <= 2 else "copy"
     if world > 1 and args.exchange in ("peer", "copy"):
         sink = PeerWgradScatter(device=dev, transport="store" if args.exchange == "peer" else "copy")
         for lin in layers:
@@ -365,7 +369,8 @@ def main():
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--exchange", default="peer", choices=["peer", "copy", "nccl"], help="wgrad exchange for --gpus > 1")
+    ap.add_argument("--exchange", default="auto", choices=["auto", "peer", "copy", "nccl"],
+                    help="wgrad exchange for --gpus > 1 (auto: GEMM stores to peers on 2 GPUs, DMA-engine copies on more)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.impl == "reference":
