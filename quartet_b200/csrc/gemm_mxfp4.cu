@@ -473,8 +473,8 @@ struct Gemm2Cfg {
     static constexpr int SFB_BYTES = SFB_BLOCKS * 1024;
     static constexpr int STAGE_BYTES = A_BYTES + B_BYTES + SFA_BYTES + SFB_BYTES;
     static constexpr int STG_BYTES = 8 * NSTG * 2048;        // epilogue staging: NSTG buffers of 2 KB per epilogue warp (8 warps)
-    static constexpr int STAGES = (232448 - STG_BYTES - 256) / STAGE_BYTES;
-    static constexpr int SMEM = STAGES * STAGE_BYTES + STG_BYTES + 256;
+    static constexpr int STAGES = (232448 - STG_BYTES - 512) / STAGE_BYTES;
+    static constexpr int SMEM = STAGES * STAGE_BYTES + STG_BYTES + 512;
     static_assert(SF_COL0 + SF_SLOTS * SF_COLS <= TMEM_COLS, "tensor memory budget");
     static_assert(SF_SLOTS < STAGES, "scale slots are recycled through the stage barriers");
     static_assert(B_BYTES % 1024 == 0, "operand stages stay 1024-byte aligned");
@@ -589,7 +589,9 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM2_THREADS, 1)
     uint64_t* full = bars;                            // local: this CTA's copies of a stage have landed
     uint64_t* empty = full + C::STAGES;               // local: the pair's MMAs are done with the stage
     uint64_t* sf_full = empty + C::STAGES;            // leader only: 8 feeder warps (both CTAs) have fed the stage
-    uint64_t* acc_full = sf_full + C::STAGES;         // local: accumulator complete
+    uint64_t* sf_land = sf_full + C::STAGES;          // local: the stage's scale blocks have landed
+    uint64_t* sf_free = sf_land + C::STAGES;          // local: the 4 feeder warps hold the stage's scales in registers
+    uint64_t* acc_full = sf_free + C::STAGES;         // local: accumulator complete
     uint64_t* acc_empty = acc_full + C::ACC_STAGES;   // leader only: 8 epilogue warps (both CTAs) have drained it
     uint32_t* s_tmem = reinterpret_cast<uint32_t*>(acc_empty + C::ACC_STAGES);
     volatile int* dead = reinterpret_cast<volatile int*>(s_tmem + 1);
@@ -600,9 +602,11 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM2_THREADS, 1)
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < C::STAGES; ++i) {
-            mbar_init(&full[i], 3);  // the A, B and scale producers
+            mbar_init(&full[i], 2);  // the A and B producers
             mbar_init(&empty[i], 1);
             mbar_init(&sf_full[i], 8);
+            mbar_init(&sf_land[i], 1);
+            mbar_init(&sf_free[i], 4);
         }
         for (int i = 0; i < C::ACC_STAGES; ++i) {
             mbar_init(&acc_full[i], 1);
@@ -650,7 +654,9 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM2_THREADS, 1)
                 const uint8_t* sfa_src = p.a_sf + (int64_t)m_blk * sf_blocks_per_rowblock * 512;
                 for (int ks = 0; ks < k_stages; ++ks) {
                     if (role == 0) TRACE(13, tr);
-                    if (!gemm_wait(&empty[s], ph ^ 1, WAIT_GEMM_EMPTY, dead)) break;
+                    // operand buffers are free once the stage's MMAs are done; the scale buffers as soon as the
+                    // feeders have them in registers, so the scale copies run several stages ahead
+                    if (!gemm_wait(role == 2 ? &sf_free[s] : &empty[s], ph ^ 1, WAIT_GEMM_EMPTY, dead)) break;
                     if (role == 0) {
                         TRACE(0, tr);
                         ++tr;
@@ -662,9 +668,9 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM2_THREADS, 1)
                     } else {
                         // the tensor copy always delivers its full box (out-of-range parts are zero-filled)
                         const int nch = min(2, p.k_chunks - 2 * ks);
-                        mbar_arrive_expect_tx(&full[s], nch * 512 + C::SFB_BYTES);
-                        bulk_load_hint(s_sfa + s * C::SFA_BYTES, sfa_src + (int64_t)ks * 1024, nch * 512, &full[s], keep);
-                        tma_load_2d_hint(s_sfb + s * C::SFB_BYTES, &tm_sfb, ks * 256, n0 / 128, &full[s], keep);
+                        mbar_arrive_expect_tx(&sf_land[s], nch * 512 + C::SFB_BYTES);
+                        bulk_load_hint(s_sfa + s * C::SFA_BYTES, sfa_src + (int64_t)ks * 1024, nch * 512, &sf_land[s], keep);
+                        tma_load_2d_hint(s_sfb + s * C::SFB_BYTES, &tm_sfb, ks * 256, n0 / 128, &sf_land[s], keep);
                     }
                     if (++s == C::STAGES) s = 0, ph ^= 1;
                 }
@@ -745,8 +751,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM2_THREADS, 1)
             for (int ks = 0; ks < k_stages; ++ks, ++it) {
                 const int s = it % C::STAGES;
                 const uint32_t ph = (it / C::STAGES) & 1;
-                if (!gemm_wait(&full[s], ph, WAIT_GEMM_FULL, dead)) break;
-                if (warp == 6 && lane == 0) { TRACE(4, it); TRACE_PEER(7, it); }
+                if (!gemm_wait(&sf_land[s], ph, WAIT_GEMM_FULL, dead)) break;
                 const int nch = min(2, p.k_chunks - 2 * ks);
                 const uint32_t sf_tmem = tmem_base + lane_base + C::SF_COL0 + (it % C::SF_SLOTS) * C::SF_COLS;
                 const uint8_t* sfa = s_sfa + s * C::SFA_BYTES + lane * 16;
@@ -765,6 +770,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM2_THREADS, 1)
                                        : 0u;
                     }
                 }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&sf_free[s]);  // the scale copies of a later stage may reuse the buffers
                 // the scale slot was last read by the MMAs of iteration it - SF_SLOTS; their completion is
                 // what the `empty` barrier of that iteration's operand stage reports
                 if (it >= (uint32_t)C::SF_SLOTS) {
@@ -784,6 +791,10 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM2_THREADS, 1)
                 }
                 tc_wait_st();
                 tc_fence_before();
+                // the scales usually sit in tensor memory before the operands arrive; the arrive below tells
+                // the MMA issuer that BOTH are there for this CTA
+                if (!gemm_wait(&full[s], ph, WAIT_GEMM_FULL, dead)) break;
+                if (warp == 6 && lane == 0) { TRACE(4, it); TRACE_PEER(7, it); }
                 __syncwarp();
                 if (lane == 0) mbar_arrive_cluster(mapa_u32(smem_u32(&sf_full[s]), 0));
                 if (warp == 6 && lane == 0) { TRACE(5, it); TRACE_PEER(8, it); }
