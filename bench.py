@@ -187,9 +187,9 @@ def gpu_arm(args):
     # owner's memory ("peer", the default), or a NCCL reduce-scatter of full partials ("nccl")
     reducer = sink = None
     if args.exchange == "auto":
-        # measured: with half of the rows remote the GEMM's own stores win; from 4 ranks on they slow the GEMM more
-        # than the DMA engines cost
-        args.exchange = "peer" if world <= 2 else "copy"
+        # measured on 2 and on 8 GPUs: the DMA-engine push costs less than the slowdown of a GEMM whose epilogue
+        # stores cross NVLink
+        args.exchange = "copy"
     if world > 1 and args.exchange in ("peer", "copy"):
         sink = PeerWgradScatter(device=dev, transport="store" if args.exchange == "peer" else "copy")
         for lin in layers:
@@ -370,7 +370,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--exchange", default="auto", choices=["auto", "peer", "copy", "nccl"],
-                    help="wgrad exchange for --gpus > 1 (auto: GEMM stores to peers on 2 GPUs, DMA-engine copies on more)")
+                    help="wgrad exchange for --gpus > 1 (auto = copy: DMA engines push each owner's rows)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.impl == "reference":

@@ -109,16 +109,11 @@ __device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, int x, int 
                  : "memory");
 }
 // --- the same copies with an L2 eviction-priority hint ---
-// Operand tiles of a GEMM are re-read by many CTAs and should stay in L2 (evict_last); its result is
-// written once and never read by the kernel, so its lines are the first to go (evict_first).
+// Operand tiles of a GEMM are re-read by many CTAs and should stay in L2 (evict_last).  (A hint on the
+// result's stores bought nothing locally and made stores into another GPU's memory several times slower.)
 __device__ __forceinline__ uint64_t l2_policy_evict_last() {
     uint64_t p;
     asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(p));
-    return p;
-}
-__device__ __forceinline__ uint64_t l2_policy_evict_first() {
-    uint64_t p;
-    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
     return p;
 }
 __device__ __forceinline__ void tma_load_2d_hint(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar, uint64_t policy) {
@@ -127,11 +122,6 @@ __device__ __forceinline__ void tma_load_2d_hint(void* dst, const CUtensorMap* m
             smem_u32(dst)),
         "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y), "l"(policy)
         : "memory");
-}
-__device__ __forceinline__ void tma_store_2d_hint(const CUtensorMap* map, int x, int y, const void* src, uint64_t policy) {
-    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group.L2::cache_hint [%0, {%2, %3}], [%1], %4;" ::"l"(map),
-                 "r"(smem_u32(src)), "r"(x), "r"(y), "l"(policy)
-                 : "memory");
 }
 __device__ __forceinline__ void bulk_load_hint(void* dst, const void* src, uint32_t bytes, uint64_t* bar, uint64_t policy) {
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;" ::"r"(

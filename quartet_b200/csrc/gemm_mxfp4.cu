@@ -217,7 +217,7 @@ __device__ __forceinline__ void epilogue_block(const uint32_t (&r)[32], const Ge
             fence_proxy_async_smem();
             __syncwarp();
             if (lane == 0) {
-                tma_store_2d_hint(tm_d, col, row0 + 16 * hf, buf, l2_policy_evict_first());
+                tma_store_2d(tm_d, col, row0 + 16 * hf, buf);
                 bulk_commit();
             }
         }
@@ -240,7 +240,7 @@ __device__ __forceinline__ void epilogue_block(const uint32_t (&r)[32], const Ge
         fence_proxy_async_smem();
         __syncwarp();
         if (lane == 0) {
-            tma_store_2d_hint(tm_d, col, row0, buf, l2_policy_evict_first());
+            tma_store_2d(tm_d, col, row0, buf);
             bulk_commit();
         }
     }
