@@ -6,6 +6,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <utility>
+
 #include "../../include/quartet_b200.h"
 
 namespace quartet {
@@ -38,6 +40,17 @@ static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t
 // ---------------------------------------------------------------------------
 #ifdef __CUDACC__
 
+template <typename... KArgs, typename... Args>
+static inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid, cfg.blockDim = block, cfg.dynamicSmemBytes = smem, cfg.stream = stream;
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr.val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = &attr, cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
+}
+
 static __device__ int32_t g_status;  // fault word of this translation unit
 
 #define QUARTET_DEFINE_STATUS_READER(NAME)                                                          \
@@ -60,6 +73,14 @@ enum : int32_t {
     WAIT_GEMM_SF = 6,
     WAIT_GEMM_ALIGN = 7,  // not a wait: dynamic shared memory was not 1024-byte aligned
 };
+
+// Programmatic dependent launch.  A kernel launched with launch_pdl() may become resident while the
+// kernel before it in the stream is still draining; pdl_wait() returns once that kernel has completed
+// and its writes are visible, so everything before it (barrier init, tensor-map prefetch, TMEM
+// allocation) overlaps the predecessor's tail and the launch latency.  No global memory is touched
+// before pdl_wait().  pdl_launch_dependents() lets the NEXT kernel do the same with this one.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
 

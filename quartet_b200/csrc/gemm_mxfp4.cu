@@ -628,6 +628,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM2_THREADS, 1)
     cluster_sync_all();  // both CTAs' barriers are initialised before any remote arrive / commit
     tc_fence_after();
     const uint32_t tmem_base = *s_tmem;
+    pdl_launch_dependents();
+    pdl_wait();  // barriers, tensor memory and the cluster are set up; global memory is touched only from here on
 
     const int m_pairs = p.m_tiles >> 1;
     const int n_tiles_total = m_pairs * p.n_tiles;
@@ -947,7 +949,8 @@ static int launch_gemm_2cta(const uint8_t* a, const uint8_t* b, void* d, const G
 #ifdef QUARTET_GEMM_TRACE
     if (const char* e = getenv("QUARTET_GEMM_MAX_CLUSTERS")) clusters = clusters < atoi(e) ? clusters : atoi(e);
 #endif
-    kern<<<clusters * 2, GEMM2_THREADS, C::SMEM, stream>>>(tm_a, tm_b, tm_d, tm_sfb, *scp, p);
+    rc = check_cuda(launch_pdl(kern, dim3(clusters * 2), dim3(GEMM2_THREADS), C::SMEM, stream, tm_a, tm_b, tm_d, tm_sfb, *scp, p), "gemm (2-CTA) launch");
+    if (rc) return rc;
 #ifdef QUARTET_GEMM_TRACE
     {
         static long long h[16][64];

@@ -63,6 +63,8 @@ __global__ void __launch_bounds__(ROWS_THREADS, F32 ? 3 : 4) quant_rows_kernel(c
         fence_mbar_init();
     }
     __syncthreads();
+    pdl_launch_dependents();
+    pdl_wait();  // the tensor this kernel reads (and the buffers it overwrites) belong to the previous kernel until here
     if (tid == 0) {
         mbar_arrive_expect_tx(bar, NBOX * 128u * p.box_rows);
 #pragma unroll
@@ -174,8 +176,7 @@ static int launch_rows(const void* x, const RowsParams& p, uint8_t* codes, uint8
     rc = check_cuda(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem), "cudaFuncSetAttribute");
     if (rc) return rc;
     dim3 grid((unsigned)(p.cols / TILE_C), (unsigned)((p.rows + TILE_R - 1) / TILE_R));
-    kern<<<grid, ROWS_THREADS, smem, stream>>>(tm_x, tm_codes, tm_mask, p);
-    return check_cuda(cudaGetLastError(), "quant_rows launch");
+    return check_cuda(launch_pdl(kern, grid, dim3(ROWS_THREADS), smem, stream, tm_x, tm_codes, tm_mask, p), "quant_rows launch");
 }
 
 static int validate_rows(const void* x, int x_dtype, int64_t rows, int64_t cols, const void* codes, const void* sf) {

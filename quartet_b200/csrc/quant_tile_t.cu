@@ -75,6 +75,8 @@ __global__ void __launch_bounds__(TT_THREADS, (SRC == SRC_F32 && DUAL) ? 2 : 4)
         fence_mbar_init();
     }
     __syncthreads();
+    pdl_launch_dependents();
+    pdl_wait();  // no global access before this point
     if (tid == 0) {
         if (SRC == SRC_MXFP4) {
             mbar_arrive_expect_tx(bar, TT * 64 + 512);
@@ -205,8 +207,7 @@ static int launch_tile_t(const void* src, const TileTParams& p, uint8_t* codes_t
     rc = check_cuda(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem), "cudaFuncSetAttribute");
     if (rc) return rc;
     dim3 grid((unsigned)(p.cols / TT), (unsigned)(p.rows / TT));
-    kern<<<grid, TT_THREADS, smem, stream>>>(tm_in, tm_out, tm_rows, p);
-    return check_cuda(cudaGetLastError(), "quant_tile_t launch");
+    return check_cuda(launch_pdl(kern, grid, dim3(TT_THREADS), smem, stream, tm_in, tm_out, tm_rows, p), "quant_tile_t launch");
 }
 
 static int validate_tile_t(const void* src, int64_t rows, int64_t cols, const void* codes_t, const void* sf_t, int rounding,
