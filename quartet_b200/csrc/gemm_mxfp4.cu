@@ -5,7 +5,8 @@
 //   D       bf16 or fp32, row-major; optional fused "mask, then rotate back by the 32-point
 //           Hadamard" epilogue (the straight-through backward of the forward quantizer).
 //
-// Structure (one CTA per SM, persistent over 128 x BN output tiles, 320 threads):
+// Structure of the one-CTA kernel (one CTA per SM, persistent over 128 x BN output tiles, 320 threads);
+// the two-CTA kernel further down keeps the roles and spreads them over a CTA pair and 512 threads:
 //   warp 0      TMA producer: per K-stage (256 elements) two tensor copies (A, B; 128B swizzle)
 //               and the stage's scale blocks as plain bulk copies, all signalling one mbarrier
 //   warp 1      allocates TMEM and issues tcgen05.mma.kind::mxf4.block_scale back to back (K = 64
@@ -17,6 +18,11 @@
 //   warps 2-5   epilogue: tcgen05.ld one accumulator row x 32 columns per thread (= exactly one
 //               Hadamard group), scale, optional mask + un-rotation, convert, stage the 32 x 32
 //               block in swizzled shared memory, TMA store
+// Two-CTA kernel (cta_group::2, 256 x 256 tile per pair): each CTA stages its own rows of A and half
+// of B; three warps issue the copies (A, B, scales); the scale copies and their tensor-memory feed run
+// ahead of the operands on their own barriers; consecutive tiles use overlapping accumulator column
+// ranges so that the next tile's MMAs start while the previous epilogue is still draining; tiles are
+// visited in compact bands; the fp32 result can be scattered by row range to per-owner destinations.
 // Every wait is bounded; a wait that gives up records itself in the fault word and the CTA
 // winds down (frees its TMEM) instead of hanging.
 #include <cstdio>
