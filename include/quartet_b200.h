@@ -178,6 +178,13 @@ int quartet_peer_copy(void* dst, const void* src, uint64_t bytes, quartet_stream
 int quartet_probe_copy_ingress(const void* src, uint64_t region, int32_t iters, int32_t stages, int32_t chunk,
                                int32_t producers, int64_t* cycles, double* bytes_per_clk_per_sm, quartet_stream_t stream);
 
+/*
+ * quartet_probe_copy_ingress without a workspace and without allocating anything: the per-SM cycle counts
+ * are kept in a device array inside the library (256 entries; a device with more SMs is rejected).
+ */
+int quartet_probe_copy_ingress_noalloc(const void* src, uint64_t region, int32_t iters, int32_t stages, int32_t chunk,
+                                       int32_t producers, double* bytes_per_clk_per_sm, quartet_stream_t stream);
+
 /* Host helpers for the blocked scale layout (`to_blocked`, benchmark_mxfp4.ipynb:1015-1016). */
 int64_t quartet_sf_offset(int64_t row, int64_t kblock, int64_t padded_kblocks);
 int64_t quartet_sf_bytes(int64_t rows, int64_t cols);

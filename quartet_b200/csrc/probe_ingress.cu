@@ -62,36 +62,76 @@ QUARTET_DEFINE_STATUS_READER(status_probe)
 
 using namespace quartet;
 
+// Per-SM cycle counts of the allocation-free entry point live here: no caller workspace, no allocation.
+constexpr int PROBE_STATIC_SMS = 256;
+static __device__ __align__(256) long long g_probe_cycles[PROBE_STATIC_SMS];
+
+static int run_probe(const void* src, uint64_t region, int32_t iters, int32_t stages, int32_t chunk, int32_t producers,
+                     long long* cycles, int sms, double* bytes_per_clk_per_sm, cudaStream_t s) {
+    const size_t smem = (size_t)producers * stages * chunk + 2 * (size_t)producers * stages * 8 + 64;
+    int rc = check_cuda(cudaFuncSetAttribute(probe_ingress_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem), "cudaFuncSetAttribute");
+    if (rc) return rc;
+    probe_ingress_kernel<<<sms, PROBE_THREADS, smem, s>>>(static_cast<const uint8_t*>(src), region, iters, stages, (uint32_t)chunk, producers, cycles);
+    if ((rc = check_cuda(cudaGetLastError(), "probe launch"))) return rc;
+    if ((rc = check_cuda(cudaStreamSynchronize(s), "probe run"))) return rc;
+    static long long host[1024];
+    if ((rc = check_cuda(cudaMemcpy(host, cycles, sizeof(long long) * sms, cudaMemcpyDeviceToHost), "probe read-back"))) return rc;
+    long long worst = 1;
+    for (int i = 0; i < sms; ++i) worst = host[i] > worst ? host[i] : worst;
+    *bytes_per_clk_per_sm = (double)iters * chunk * producers / (double)worst;
+    return QUARTET_OK;
+}
+
+static int validate_probe(const void* src, uint64_t region, int32_t iters, int32_t stages, int32_t chunk, int32_t producers,
+                          const void* result, int* sms) {
+    if (!src || !result) return fail(QUARTET_E_NULL, "src and the result pointer must be non-NULL");
+    if (producers < 1 || producers > PROBE_MAX_PRODUCERS || stages < 1 || stages > 32 || iters < 1)
+        return fail(QUARTET_E_ARG, "need 1..%d producers, 1..32 stages, iters >= 1", PROBE_MAX_PRODUCERS);
+    if (chunk < 128 || chunk % 128 || region < 4ull * chunk || !aligned16(src))
+        return fail(QUARTET_E_ARG, "chunk must be a positive multiple of 128 bytes, region >= 4 chunks, src 16-byte aligned");
+    if ((size_t)producers * stages * chunk + 2 * (size_t)producers * stages * 8 + 64 > 220 * 1024)
+        return fail(QUARTET_E_ARG, "producers * stages * chunk exceeds the shared memory of an SM");
+    int rc = bind_context_of(src);
+    if (rc) return rc;
+    if ((rc = check_device())) return rc;
+    if ((rc = device_sm_count(sms))) return rc;
+    if (*sms > 1024) return fail(QUARTET_E_ARG, "more SMs than the probe's host buffer holds");
+    return QUARTET_OK;
+}
+
 // bytes_per_clk_per_sm = iters * chunk * producers / (slowest CTA's cycles).  `src` is a device buffer of
 // `region` bytes (keep it below the L2 size to measure the L2 -> SM path), `cycles` a device array of
 // one int64 per SM used as scratch for the result.
 extern "C" __attribute__((visibility("default"))) int quartet_probe_copy_ingress(const void* src, uint64_t region, int32_t iters, int32_t stages,
                                                                                  int32_t chunk, int32_t producers, int64_t* cycles,
                                                                                  double* bytes_per_clk_per_sm, quartet_stream_t stream) {
-    if (!src || !cycles || !bytes_per_clk_per_sm) return fail(QUARTET_E_NULL, "src, cycles and the result pointer must be non-NULL");
-    if (producers < 1 || producers > PROBE_MAX_PRODUCERS || stages < 1 || stages > 32 || iters < 1)
-        return fail(QUARTET_E_ARG, "need 1..%d producers, 1..32 stages, iters >= 1", PROBE_MAX_PRODUCERS);
-    if (chunk < 128 || chunk % 128 || region < 4ull * chunk || !aligned16(src))
-        return fail(QUARTET_E_ARG, "chunk must be a positive multiple of 128 bytes, region >= 4 chunks, src 16-byte aligned");
-    const size_t smem = (size_t)producers * stages * chunk + 2 * (size_t)producers * stages * 8 + 64;
-    if (smem > 220 * 1024) return fail(QUARTET_E_ARG, "producers * stages * chunk exceeds the shared memory of an SM");
-    int rc = bind_context_of(src);
-    if (rc) return rc;
-    if ((rc = check_device())) return rc;
+    if (!cycles) return fail(QUARTET_E_NULL, "cycles must be non-NULL");
     int sms = 0;
-    if ((rc = device_sm_count(&sms))) return rc;
-    if ((rc = check_cuda(cudaFuncSetAttribute(probe_ingress_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem), "cudaFuncSetAttribute")))
-        return rc;
-    cudaStream_t s = static_cast<cudaStream_t>(stream);
-    probe_ingress_kernel<<<sms, PROBE_THREADS, smem, s>>>(static_cast<const uint8_t*>(src), region, iters, stages, (uint32_t)chunk, producers,
-                                                          reinterpret_cast<long long*>(cycles));
-    if ((rc = check_cuda(cudaGetLastError(), "probe launch"))) return rc;
-    if ((rc = check_cuda(cudaStreamSynchronize(s), "probe run"))) return rc;
-    static long long host[1024];
-    if (sms > 1024) return fail(QUARTET_E_ARG, "more SMs than the probe's host buffer holds");
-    if ((rc = check_cuda(cudaMemcpy(host, cycles, sizeof(long long) * sms, cudaMemcpyDeviceToHost), "probe read-back"))) return rc;
-    long long worst = 1;
-    for (int i = 0; i < sms; ++i) worst = host[i] > worst ? host[i] : worst;
-    *bytes_per_clk_per_sm = (double)iters * chunk * producers / (double)worst;
-    return QUARTET_OK;
+    int rc = validate_probe(src, region, iters, stages, chunk, producers, bytes_per_clk_per_sm, &sms);
+    if (rc) return rc;
+    return run_probe(src, region, iters, stages, chunk, producers, reinterpret_cast<long long*>(cycles), sms, bytes_per_clk_per_sm,
+                     static_cast<cudaStream_t>(stream));
+}
+
+// The same measurement without any workspace from the caller and without allocating: the per-SM cycle
+// counts go to the file-scope device array above, whose address is looked up once per device.  A device
+// with more SMs than the array holds is rejected.
+extern "C" __attribute__((visibility("default"))) int quartet_probe_copy_ingress_noalloc(const void* src, uint64_t region, int32_t iters,
+                                                                                         int32_t stages, int32_t chunk, int32_t producers,
+                                                                                         double* bytes_per_clk_per_sm, quartet_stream_t stream) {
+    int sms = 0;
+    int rc = validate_probe(src, region, iters, stages, chunk, producers, bytes_per_clk_per_sm, &sms);
+    if (rc) return rc;
+    if (sms > PROBE_STATIC_SMS)
+        return fail(QUARTET_E_ARG, "the device has %d SMs, the built-in scratch array holds %d", sms, PROBE_STATIC_SMS);
+    static thread_local int cached_dev = -1;
+    static thread_local long long* scratch = nullptr;
+    int dev = 0;
+    if ((rc = check_cuda(cudaGetDevice(&dev), "cudaGetDevice"))) return rc;
+    if (dev != cached_dev) {  // set-up: the symbol's address on this device
+        void* addr = nullptr;
+        if ((rc = check_cuda(cudaGetSymbolAddress(&addr, g_probe_cycles), "cudaGetSymbolAddress"))) return rc;
+        scratch = static_cast<long long*>(addr), cached_dev = dev;
+    }
+    return run_probe(src, region, iters, stages, chunk, producers, scratch, sms, bytes_per_clk_per_sm, static_cast<cudaStream_t>(stream));
 }

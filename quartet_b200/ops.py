@@ -225,6 +225,19 @@ def probe_copy_ingress(region_mb=48, iters=4000, stages=6, chunk=16384, producer
     return out.value
 
 
+def probe_copy_ingress_noalloc(src, iters=4000, stages=6, chunk=16384, producers=2):
+    """`probe_copy_ingress` on a caller-provided uint8 device tensor; neither this wrapper nor the library allocates."""
+    import ctypes as C
+
+    _need_cuda(src)
+    out = C.c_double(0.0)
+    with torch.cuda.device(src.device):
+        rc = _lib.load().quartet_probe_copy_ingress_noalloc(_ptr(src), src.numel() * src.element_size(), iters, stages, chunk, producers,
+                                                            C.byref(out), _stream())
+    _lib.check(rc, "quartet_probe_copy_ingress_noalloc")
+    return out.value
+
+
 def unrotate_mask(g, mask=None, had_scale=HAD_SCALE_BF16, out_dtype=None):
     """((g * mask).view(-1, 32) @ H^T).view_as(g)"""
     _need_cuda(g, mask)
