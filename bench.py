@@ -8,7 +8,8 @@ Workload ("llama7b_linears_16384tok"): the four linear layers of a 7B Llama bloc
 ~N(0,1e-3); synthetic, seeded.  One step = all four layers once, through
 quartet_b200.quantization.QuantizedLinear (forward + backward).  Token rows are sharded over the
 GPUs (weak scaling: 16384 tokens on every GPU); the per-GPU weight-gradient partials are averaged
-with an NCCL reduce-scatter inside the step.  Metric: model FLOP/s = 6*M*N*K per layer, summed over
+inside the step, every rank ending up with its row shard (--exchange: rows pushed into their owner's
+memory by the DMA engines or by the GEMM's own stores, or an NCCL reduce-scatter).  Metric: model FLOP/s = 6*M*N*K per layer, summed over
 layers and GPUs.
 
 `--impl reference` times the reference's own pseudo-quantized arithmetic for the same layers on the
