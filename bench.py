@@ -161,7 +161,7 @@ def gpu_arm(args):
         dist.barrier()
     from quartet_b200 import ops
     from quartet_b200.quantization import BACKWARD_SCHEMES, QUANTIZER_CLASSES, QuantizedLinear
-    from quartet_b200.shard import PeerWgradScatter, WgradReduceScatter
+    from quartet_b200.shard import PeerSetupError, PeerWgradScatter, WgradReduceScatter
     from quartet_b200.staging import HostStager
 
     # ---- model + data (seeded; weights identical on every rank, activations differ per rank) ----
@@ -192,11 +192,17 @@ def gpu_arm(args):
         # stores cross NVLink
         args.exchange = "copy"
     if world > 1 and args.exchange in ("peer", "copy"):
-        sink = PeerWgradScatter(device=dev, transport="store" if args.exchange == "peer" else "copy")
-        for lin in layers:
-            sink.prepare(lin.weight)
-            lin.wgrad_sink = sink
-    elif world > 1:
+        try:
+            sink = PeerWgradScatter(device=dev, transport="store" if args.exchange == "peer" else "copy")
+            for lin in layers:
+                sink.prepare(lin.weight)
+            for lin in layers:
+                lin.wgrad_sink = sink
+        except PeerSetupError as exc:  # raised on every rank alike: fall back to the library collective everywhere
+            if rank == 0:
+                print(f"bench: {exc}; using the NCCL reduce-scatter", file=sys.stderr)
+            sink, args.exchange = None, "nccl"
+    if world > 1 and sink is None:
         reducer = WgradReduceScatter(world)
 
     # ---- count launches of this library's kernels and time them per kind ----

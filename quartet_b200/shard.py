@@ -63,6 +63,10 @@ class WgradReduceScatter:
         return out
 
 
+class PeerSetupError(RuntimeError):
+    """Raised on EVERY rank when any rank failed to allocate or map the receive buffers."""
+
+
 class PeerWgradScatter:
     """The weight-gradient exchange folded into the wgrad GEMM.
 
@@ -116,23 +120,44 @@ class PeerWgradScatter:
             raise ValueError(f"weight [{rows}, {cols}] {weight.dtype} cannot be scattered over {self.world} ranks")
         rpo = rows // self.world
         slot_bytes = rpo * cols * 4
-        mine, handles = [], []
-        for _ in range(2):
-            ptr, h = self.ops.peer_alloc(self.world * slot_bytes, self.device)
-            mine.append(ptr), handles.append(h)
+        # Every rank walks through the same collectives whatever fails locally, and all ranks agree on
+        # the outcome before anyone raises: a rank that cannot allocate or map must not leave the others
+        # waiting in a collective.
+        mine, handles, opened, error = [], [], [], None
+        try:
+            for _ in range(2):
+                ptr, h = self.ops.peer_alloc(self.world * slot_bytes, self.device)
+                mine.append(ptr), handles.append(h)
+        except Exception as exc:  # noqa: BLE001 - reported after the agreement below
+            error = exc
         gathered = [None] * self.world
-        dist.all_gather_object(gathered, handles, group=self.group)
-        dst, opened = [], []
-        for parity in range(2):
-            bases = []
-            for o in range(self.world):
-                if o == self.rank:
-                    bases.append(mine[parity])
-                else:
-                    p = self.ops.peer_open(gathered[o][parity], self.device)
-                    opened.append(p)
-                    bases.append(p)
-            dst.append([b + self.rank * slot_bytes for b in bases])
+        dist.all_gather_object(gathered, handles if error is None else None, group=self.group)
+        dst = []
+        if error is None and all(g is not None for g in gathered):
+            try:
+                for parity in range(2):
+                    bases = []
+                    for o in range(self.world):
+                        if o == self.rank:
+                            bases.append(mine[parity])
+                        else:
+                            p = self.ops.peer_open(gathered[o][parity], self.device)
+                            opened.append(p)
+                            bases.append(p)
+                    dst.append([b + self.rank * slot_bytes for b in bases])
+            except Exception as exc:  # noqa: BLE001
+                error = exc
+        elif error is None:
+            error = RuntimeError("another rank could not allocate its receive buffers")
+        ok = torch.tensor([0.0 if error is not None else 1.0], device=self.device)
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=self.group)
+        if ok.item() < 1.0:
+            for p in opened:
+                self.ops.peer_close(p, self.device)
+            dist.barrier(group=self.group)  # nobody frees a buffer a peer still has mapped
+            for p in mine:
+                self.ops.peer_free(p, self.device)
+            raise PeerSetupError(f"peer receive buffers could not be set up on every rank: {error or 'failure on another rank'}")
         plan = {"rows": rows, "cols": cols, "rpo": rpo, "mine": mine, "dst": dst, "opened": opened, "uses": 0}
         self.plans[key] = plan
         return plan
