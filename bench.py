@@ -30,7 +30,7 @@ sys.path.insert(0, ROOT)
 
 LAYERS = [("qkv", 4096, 12288), ("o", 4096, 4096), ("gate_up", 4096, 22016), ("down", 11008, 4096)]
 TOKENS = 16384
-CPU_SAMPLE_TOKENS = 512
+CPU_SAMPLE_TOKENS = int(os.environ.get("QUARTET_BENCH_CPU_TOKENS", "512"))  # token sample of the CPU arm (the tests shrink it)
 WORKLOAD = "llama7b_linears_16384tok"
 METRIC = "quantized_linear_fwd_bwd_tflops"
 
