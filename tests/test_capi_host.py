@@ -55,3 +55,12 @@ def test_rejections(lib):
     assert lib.quartet_dequant(q, p, 1, 32, 1.0, p, 1, None) == -3
     with pytest.raises(ValueError):
         _lib.check(-2, "x")
+
+
+def test_host_stager_has_no_cpu_path():
+    import torch
+
+    from quartet_b200.staging import HostStager
+
+    with pytest.raises(RuntimeError):
+        HostStager(torch.device("cpu"))

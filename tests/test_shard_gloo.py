@@ -41,6 +41,23 @@ def _worker(rank, world, port, q):
     full = (e.T @ x) / world
     rows = n // world
     ok = torch.allclose(a, full[rank * rows:(rank + 1) * rows], atol=1e-4) and torch.allclose(b, 2 * a, atol=1e-4)
+    # the peer-memory exchange in host arithmetic: slot r of this owner's receive buffer holds the owner's row range of
+    # rank r's partial; the slots are added in rank order and scaled by 1/world -- the same shard as above
+    parts = [torch.empty_like(dw_part) for _ in range(world)]
+    dist.all_gather(parts, dw_part)
+    slots = torch.stack([part_r[rank * rows:(rank + 1) * rows] for part_r in parts])
+    acc = slots[0].clone()
+    for r in range(1, world):
+        acc = acc + slots[r]
+    ok = ok and torch.allclose(acc * (1.0 / world), a, atol=1e-4)
+    # ... and the GPU implementation refuses a host backend instead of falling back to something else
+    from quartet_b200.shard import PeerWgradScatter
+
+    try:
+        PeerWgradScatter()
+        ok = False
+    except RuntimeError:
+        pass
     # per-rank quantization of the transposed operand equals the single-process result group for group
     h = rm.hadamard32()
     u = torch.rand(n, m, generator=gen)
