@@ -172,15 +172,23 @@ int quartet_peer_copy(void* dst, const void* src, uint64_t bytes, quartet_stream
 /*
  * Measurement aid (no reference counterpart): bytes per clock one SM takes in through bulk asynchronous
  * copies from `src` (`region` bytes, keep it L2-resident), with `producers` (1..4) issuing threads per SM,
- * each running a ring of `stages` buffers of `chunk` bytes for `iters` copies.  `cycles` is a device
- * array of one int64 per SM; the call synchronises the stream and writes the result to the host.
+ * each running a ring of `stages` buffers of `chunk` bytes for `iters` copies.  `src` must be 128-byte
+ * aligned, `chunk` a multiple of 128 and `region` at least 4 chunks; every copy stays inside the region.
+ * `cycles` is a device array of one int64 per SM; the call synchronises the stream and writes the result
+ * to the host.
  */
 int quartet_probe_copy_ingress(const void* src, uint64_t region, int32_t iters, int32_t stages, int32_t chunk,
                                int32_t producers, int64_t* cycles, double* bytes_per_clk_per_sm, quartet_stream_t stream);
 
 /*
- * quartet_probe_copy_ingress without a workspace and without allocating anything: the per-SM cycle counts
- * are kept in a device array inside the library (256 entries; a device with more SMs is rejected).
+ * quartet_probe_copy_ingress for callers that cannot allocate device memory (no counterpart in the
+ * reference): code running while the framework's allocator is frozen, plugins that work inside buffers
+ * their host application handed them, hooks that run when the device is almost full.  No workspace
+ * argument and no allocation of any kind: the per-SM cycle counts live in a 256-entry device array
+ * inside the library (2 KB held by every GPU that loads it, until exit).  A device with more than 256 SMs
+ * is rejected with QUARTET_E_ARG.  The first call of a thread on a device looks up the array's address;
+ * make it before any stream capture.  All calls on a device share the one array: calls that overlap on
+ * the GPU (two streams, two host threads) race on it and must be serialised by the caller.
  */
 int quartet_probe_copy_ingress_noalloc(const void* src, uint64_t region, int32_t iters, int32_t stages, int32_t chunk,
                                        int32_t producers, double* bytes_per_clk_per_sm, quartet_stream_t stream);

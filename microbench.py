@@ -1,11 +1,11 @@
 """Kernel-level micro-benchmark of the path, one kernel per run:
 
-    python -m quartet_b200.microbench --kernel quant_fwd  --rows 16384 --cols 4096 [--dtype bf16|f32]
-    python -m quartet_b200.microbench --kernel quant_bwd  --rows 16384 --cols 12288 [--rounding 1]
-    python -m quartet_b200.microbench --kernel quant_bwd_t --rows 16384 --cols 12288
-    python -m quartet_b200.microbench --kernel requant_t  --rows 16384 --cols 4096
-    python -m quartet_b200.microbench --kernel gemm --m 16384 --n 12288 --k 4096 [--fused-unrotate]
-    python -m quartet_b200.microbench --sweep            # quantize-only bandwidth sweep
+    python microbench.py --kernel quant_fwd  --rows 16384 --cols 4096 [--dtype bf16|f32]
+    python microbench.py --kernel quant_bwd  --rows 16384 --cols 12288 [--rounding 1]
+    python microbench.py --kernel quant_bwd_t --rows 16384 --cols 12288
+    python microbench.py --kernel requant_t  --rows 16384 --cols 4096
+    python microbench.py --kernel gemm --m 16384 --n 12288 --k 4096 [--fused-unrotate]
+    python microbench.py --sweep            # quantize-only bandwidth sweep
 
 Timing: CUDA events on the launching stream, `--warmup` untimed launches, then `--iters` timed
 launches with a 256 MB write between launches to flush L2 (excluded from the timing).  Inputs are
@@ -17,17 +17,21 @@ from __future__ import annotations
 import argparse
 import json
 import os
+import sys
 
 import torch
 
-from . import ops
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+from quartet_b200 import ops  # noqa: E402
 
 BYTES_PER_ELEM = {"quant_fwd": 0.5 + 1 / 32 + 1 / 8, "quant_bwd": 0.5 + 1 / 32, "quant_bwd_t": 0.5 + 1 / 32,
                   "quant_bwd_dual": 2 * (0.5 + 1 / 32)}
 
 
 def _peaks():
-    path = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "MEASURED_PEAKS.json")
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     try:
         return json.load(open(path))
     except OSError:

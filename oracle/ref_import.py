@@ -33,7 +33,9 @@ def load(ref_src: str | None = None):
     global _REF
     if _REF is not None:
         return _REF
-    ref_src = ref_src or os.environ.get("QUARTET_REF", "/root/reference/src")
+    ref_src = ref_src or os.environ.get("QUARTET_REF")
+    if not ref_src:
+        raise FileNotFoundError("set QUARTET_REF to the `src` directory of a reference checkout")
     if not os.path.isdir(ref_src):
         raise FileNotFoundError(ref_src)
     os.environ["TRITON_INTERPRET"] = "1"

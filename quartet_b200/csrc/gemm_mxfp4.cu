@@ -25,24 +25,10 @@
 // visited in compact bands; the fp32 result can be scattered by row range to per-owner destinations.
 // Every wait is bounded; a wait that gives up records itself in the fault word and the CTA
 // winds down (frees its TMEM) instead of hanging.
-#include <cstdio>
-#include <cstdlib>
-
 #include "common.cuh"
 #include "quant_math.cuh"
 
 namespace quartet {
-
-// Pipeline event trace, compiled in only with -DQUARTET_GEMM_TRACE (a tuning aid): CTA 0 (and its
-// peer, CTA 1) record the SM clock of up to 64 stage iterations per event kind.
-#ifdef QUARTET_GEMM_TRACE
-__device__ long long g_trace[16][64];
-#define TRACE(kind, idx) do { if (blockIdx.x == 0 && (idx) < 64) g_trace[kind][idx] = clock64(); } while (0)
-#define TRACE_PEER(kind, idx) do { if (blockIdx.x == 1 && (idx) < 64) g_trace[kind][idx] = clock64(); } while (0)
-#else
-#define TRACE(kind, idx)
-#define TRACE_PEER(kind, idx)
-#endif
 
 constexpr int BM = 128;
 constexpr int BK_BYTES = 128;   // 256 e2m1 elements per stage along K
@@ -653,7 +639,6 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM2_THREADS, 1)
             const int role = warp == 0 ? 0 : (warp == 10 ? 1 : 2);
             const uint64_t keep = l2_policy_evict_last();  // operands and scales are re-read by other CTAs
             uint32_t s = 0, ph = 0;
-            [[maybe_unused]] uint32_t tr = 0;
             for (int tile = cluster_id; tile < n_tiles_total && !*dead; tile += n_clusters) {
                 int m_pair, n_blk;
                 tile_coords(tile, m_pairs, p.n_tiles, m_pair, n_blk);
@@ -661,13 +646,10 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM2_THREADS, 1)
                 const int m0 = m_blk * BM, n0 = n_blk * BN;
                 const uint8_t* sfa_src = p.a_sf + (int64_t)m_blk * sf_blocks_per_rowblock * 512;
                 for (int ks = 0; ks < k_stages; ++ks) {
-                    if (role == 0) TRACE(13, tr);
                     // operand buffers are free once the stage's MMAs are done; the scale buffers as soon as the
                     // feeders have them in registers, so the scale copies run several stages ahead
                     if (!gemm_wait(role == 2 ? &sf_free[s] : &empty[s], ph ^ 1, WAIT_GEMM_EMPTY, dead)) break;
                     if (role == 0) {
-                        TRACE(0, tr);
-                        ++tr;
                         mbar_arrive_expect_tx(&full[s], C::A_BYTES);
                         tma_load_2d_hint(s_a + s * C::A_BYTES, &tm_a, ks * BK_BYTES, m0, &full[s], keep);
                     } else if (role == 1) {
@@ -689,7 +671,6 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM2_THREADS, 1)
         if (leader) {
             // ring positions are kept as (index, phase) pairs: no division in the issue loop
             uint32_t s = 0, ph = 0, slot = 0, as = 0, aph = 0, acc_it = 0;
-            [[maybe_unused]] uint32_t tr = 0;
             const uint32_t idesc0 = make_idesc2(BN, 0), idesc1 = make_idesc2(BN, 2);
             const uint32_t a_base = smem_u32(s_a), b_base = smem_u32(s_b);
             const uint32_t empty_own = smem_u32(&empty[0]), accf_own = smem_u32(&acc_full[0]);
@@ -706,10 +687,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM2_THREADS, 1)
                     const uint32_t slot1 = (slot + 1 == C::SF_SLOTS) ? 0 : slot + 1;
                     // the feeders arrive only after the stage's copies have landed in BOTH CTAs, so this
                     // one barrier per stage covers operands and scales
-                    TRACE(1, tr);
                     if (!gemm_wait(&sf_full[s], ph, WAIT_GEMM_SF, dead)) break;
                     if (n2 == 2 && !mbar_try_wait(&sf_full[s1], ph1)) n2 = 1;  // pair up only if the next stage is ready too
-                    TRACE(2, tr);
                     tc_fence_after();
                     if (elect_one()) {
 #pragma unroll
@@ -733,9 +712,6 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM2_THREADS, 1)
                         }
                     }
                     __syncwarp();
-                    TRACE(3, tr);
-                    if (n2 == 2) TRACE(11, tr + 1);
-                    tr += n2;
                     for (int h = 0; h < n2; ++h) {
                         if (++s == C::STAGES) s = 0, ph ^= 1;
                         if (++slot == C::SF_SLOTS) slot = 0;
@@ -802,10 +778,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM2_THREADS, 1)
                 // the scales usually sit in tensor memory before the operands arrive; the arrive below tells
                 // the MMA issuer that BOTH are there for this CTA
                 if (!gemm_wait(&full[s], ph, WAIT_GEMM_FULL, dead)) break;
-                if (warp == 6 && lane == 0) { TRACE(4, it); TRACE_PEER(7, it); }
                 __syncwarp();
                 if (lane == 0) mbar_arrive_cluster(mapa_u32(smem_u32(&sf_full[s]), 0));
-                if (warp == 6 && lane == 0) { TRACE(5, it); TRACE_PEER(8, it); }
             }
         }
     } else if ((warp >= 2 && warp <= 5) || warp >= 11) {
@@ -823,7 +797,6 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM2_THREADS, 1)
             const int n0 = n_blk * BN;
             const int as = acc_it % C::ACC_STAGES;
             if (!gemm_wait(&acc_full[as], (acc_it / C::ACC_STAGES) & 1, WAIT_GEMM_ACC_FULL, dead)) break;
-            if (warp == 2 && lane == 0) TRACE(9, acc_it);
             tc_fence_after();
             const int64_t row = (int64_t)(m_blk * BM + q * 32) + lane;
             // where this warp's 32 rows are stored: the one output, or their owner's slice of it
@@ -873,7 +846,6 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM2_THREADS, 1)
                 __syncwarp();
                 if (lane == 0) mbar_arrive_cluster(mapa_u32(smem_u32(&acc_empty[as]), 0));
             }
-            if (warp == 2 && lane == 0) TRACE(10, acc_it);
         }
         if (lane == 0) bulk_wait0();
     }
@@ -948,35 +920,11 @@ static int launch_gemm_2cta(const uint8_t* a, const uint8_t* b, void* d, const G
         if ((rc = check_cuda(cudaOccupancyMaxActiveClusters(&n, kern, &cfg), "cudaOccupancyMaxActiveClusters"))) return rc;
         if (n < 1) return fail(QUARTET_E_CUDA, "no CTA pair can be resident");
         cached_dev = dev, cached_clusters = n;
-        if (getenv("QUARTET_GEMM_VERBOSE")) fprintf(stderr, "quartet: %d SMs, %d resident CTA pairs\n", sms, n);
     }
     const int pair_tiles = (p.m_tiles / 2) * p.n_tiles;
-    int clusters = pair_tiles < cached_clusters ? pair_tiles : cached_clusters;
-#ifdef QUARTET_GEMM_TRACE
-    if (const char* e = getenv("QUARTET_GEMM_MAX_CLUSTERS")) clusters = clusters < atoi(e) ? clusters : atoi(e);
-#endif
+    const int clusters = pair_tiles < cached_clusters ? pair_tiles : cached_clusters;
     rc = check_cuda(launch_pdl(kern, dim3(clusters * 2), dim3(GEMM2_THREADS), C::SMEM, stream, tm_a, tm_b, tm_d, tm_sfb, *scp, p), "gemm (2-CTA) launch");
     if (rc) return rc;
-#ifdef QUARTET_GEMM_TRACE
-    {
-        static long long h[16][64];
-        cudaDeviceSynchronize();
-        if (cudaMemcpyFromSymbol(h, g_trace, sizeof(h)) == cudaSuccess) {
-            const char* names[9] = {"prod:empty_ok", "mma:full_ok", "mma:sf_ok", "mma:commit", "feed:full_ok", "feed:arrive",
-                                    "PEER prod:empty_ok", "PEER feed:full_ok", "PEER feed:arrive"};
-            // per stage: producer issue time, then deltas: landed (feeder saw full), fed (feeder arrive), MMA saw
-            // sf_full, committed; `paired` marks the second stage of a two-stage trip; reuse = producer issue of it+STAGES
-            for (int i = 0; i < 40; ++i) {
-                const bool second = h[11][i] != 0 && h[1][i] == 0;
-                const long long issue = h[0][i], commit = second ? h[11][i] : h[3][i];
-                fprintf(stderr, "it %2d issue=%7lld land=+%5lld fed=+%4lld | mma %s commit=+%5lld (from fed) | reissue=+%5lld (from commit)\n", i,
-                        issue - h[0][0], h[4][i] - issue, h[5][i] - h[4][i], second ? "2nd" : "1st", commit - h[5][i],
-                        i + C::STAGES < 64 ? h[0][i + C::STAGES] - commit : 0);
-            }
-            for (int i = 0; i < 4; ++i) fprintf(stderr, "tile %d epi:acc_full_ok=%lld epi:done=%lld\n", i, h[9][i] - h[0][0], h[10][i] - h[0][0]);
-        }
-    }
-#endif
     return check_cuda(cudaGetLastError(), "gemm (2-CTA) launch");
 }
 
@@ -1036,20 +984,10 @@ extern "C" __attribute__((visibility("default"))) int quartet_gemm_mxfp4_tn(cons
     p.alpha = alpha, p.mask = mask, p.had_scale = had_scale;
     p.d_f32 = d_dtype == QUARTET_F32;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    // Tile width: 256 unless the output is narrow or not a multiple of 256.  QUARTET_GEMM_BN=128|256
-    // overrides the choice (tuning aid).
-    static const int forced_bn = [] {
-        const char* e = getenv("QUARTET_GEMM_BN");
-        return e ? atoi(e) : 0;
-    }();
-    static const int forced_cta = [] {
-        const char* e = getenv("QUARTET_GEMM_CTAS");
-        return e ? atoi(e) : 0;
-    }();
-    const bool wide = forced_bn ? forced_bn >= 256 : (N % 256 == 0 || N > 1024);
-    // CTA pairs need an even number of 128-row tiles; QUARTET_GEMM_CTAS=1|2 overrides (tuning aid).
-    const bool pair = forced_cta ? forced_cta == 2 : true;
-    if (pair && wide && M % 256 == 0) {
+    // Tile width: 256 unless the output is narrow and not a multiple of 256; CTA pairs need an even number
+    // of 128-row tiles.
+    const bool wide = N % 256 == 0 || N > 1024;
+    if (wide && M % 256 == 0) {
         return launch_gemm_2cta<256>(a, b, d, p, s);
     }
     if (wide) return launch_gemm<256>(a, b, d, p, s);

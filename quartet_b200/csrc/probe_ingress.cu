@@ -14,15 +14,18 @@ namespace quartet {
 
 constexpr int PROBE_THREADS = 256;
 constexpr int PROBE_MAX_PRODUCERS = 4;
+constexpr int PROBE_MAX_SMS = 1024;  // size of the host read-back buffer (a local array of the call)
 
 __global__ void __launch_bounds__(PROBE_THREADS, 1)
     probe_ingress_kernel(const uint8_t* __restrict__ src, uint64_t region, int iters, int stages, uint32_t chunk, int producers,
                          long long* __restrict__ cycles) {
     extern __shared__ __align__(1024) uint8_t smem[];
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + (size_t)producers * stages * chunk);
+    unsigned long long* s_elapsed = reinterpret_cast<unsigned long long*>(bars + 2 * producers * stages);
     const int w = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (threadIdx.x == 0) {
         for (int i = 0; i < 2 * producers * stages; ++i) mbar_init(&bars[i], 1);
+        *s_elapsed = 0;
         fence_mbar_init();
     }
     __syncthreads();
@@ -31,15 +34,18 @@ __global__ void __launch_bounds__(PROBE_THREADS, 1)
         uint64_t* full = bars + w * 2 * stages;
         uint64_t* empty = full + stages;
         uint8_t* buf = smem + (size_t)w * stages * chunk;
-        uint64_t off = ((((uint64_t)blockIdx.x * 7919u + (uint64_t)w * 104729u) * chunk) % (region - chunk)) & ~uint64_t(127);
+        // Source offsets walk over `slots` chunk-sized, chunk-aligned positions (chunk is a multiple of 128
+        // bytes), always reduced modulo `slots`: every copy lies inside [src, src + region) and starts on a
+        // 128-byte boundary whatever the region size.
+        const uint64_t slots = region / chunk;
+        uint64_t slot = ((uint64_t)blockIdx.x * 7919u + (uint64_t)w * 104729u) % slots;
         int s = 0;
         uint32_t ph = 0;
         for (int k = 0; k < iters; ++k) {
             if (!mbar_wait(&empty[s], ph ^ 1, WAIT_QUANT_LOAD)) break;
             mbar_arrive_expect_tx(&full[s], chunk);
-            bulk_load(buf + (size_t)s * chunk, src + off, chunk, &full[s]);
-            off += (uint64_t)chunk * 149u;
-            if (off + chunk > region) off -= region - chunk;
+            bulk_load(buf + (size_t)s * chunk, src + slot * chunk, chunk, &full[s]);
+            slot = (slot + 149u) % slots;
             if (++s == stages) s = 0, ph ^= 1;
         }
     } else if (lane == 0 && w >= PROBE_MAX_PRODUCERS && w < PROBE_MAX_PRODUCERS + producers) {
@@ -52,8 +58,11 @@ __global__ void __launch_bounds__(PROBE_THREADS, 1)
             mbar_arrive(&empty[s]);
             if (++s == stages) s = 0, ph ^= 1;
         }
-        if (w == PROBE_MAX_PRODUCERS) cycles[blockIdx.x] = clock64() - t0;
+        // the CTA's time is that of its slowest ring
+        atomicMax(s_elapsed, (unsigned long long)(clock64() - t0));
     }
+    __syncthreads();
+    if (threadIdx.x == 0) cycles[blockIdx.x] = (long long)*s_elapsed;
 }
 
 QUARTET_DEFINE_STATUS_READER(status_probe)
@@ -62,7 +71,9 @@ QUARTET_DEFINE_STATUS_READER(status_probe)
 
 using namespace quartet;
 
-// Per-SM cycle counts of the allocation-free entry point live here: no caller workspace, no allocation.
+// Scratch of the allocation-free entry point: one cycle count per SM, at most PROBE_STATIC_SMS of them.
+// The array is part of the library image, so every GPU that loads the library holds these 2 KB until
+// the process exits.  All calls on a device share it.
 constexpr int PROBE_STATIC_SMS = 256;
 static __device__ __align__(256) long long g_probe_cycles[PROBE_STATIC_SMS];
 
@@ -74,7 +85,7 @@ static int run_probe(const void* src, uint64_t region, int32_t iters, int32_t st
     probe_ingress_kernel<<<sms, PROBE_THREADS, smem, s>>>(static_cast<const uint8_t*>(src), region, iters, stages, (uint32_t)chunk, producers, cycles);
     if ((rc = check_cuda(cudaGetLastError(), "probe launch"))) return rc;
     if ((rc = check_cuda(cudaStreamSynchronize(s), "probe run"))) return rc;
-    static long long host[1024];
+    long long host[PROBE_MAX_SMS];
     if ((rc = check_cuda(cudaMemcpy(host, cycles, sizeof(long long) * sms, cudaMemcpyDeviceToHost), "probe read-back"))) return rc;
     long long worst = 1;
     for (int i = 0; i < sms; ++i) worst = host[i] > worst ? host[i] : worst;
@@ -87,15 +98,15 @@ static int validate_probe(const void* src, uint64_t region, int32_t iters, int32
     if (!src || !result) return fail(QUARTET_E_NULL, "src and the result pointer must be non-NULL");
     if (producers < 1 || producers > PROBE_MAX_PRODUCERS || stages < 1 || stages > 32 || iters < 1)
         return fail(QUARTET_E_ARG, "need 1..%d producers, 1..32 stages, iters >= 1", PROBE_MAX_PRODUCERS);
-    if (chunk < 128 || chunk % 128 || region < 4ull * chunk || !aligned16(src))
-        return fail(QUARTET_E_ARG, "chunk must be a positive multiple of 128 bytes, region >= 4 chunks, src 16-byte aligned");
+    if (chunk < 128 || chunk % 128 || region < 4ull * chunk || (reinterpret_cast<uintptr_t>(src) & 127u))
+        return fail(QUARTET_E_ARG, "chunk must be a positive multiple of 128 bytes, region >= 4 chunks, src 128-byte aligned");
     if ((size_t)producers * stages * chunk + 2 * (size_t)producers * stages * 8 + 64 > 220 * 1024)
         return fail(QUARTET_E_ARG, "producers * stages * chunk exceeds the shared memory of an SM");
     int rc = bind_context_of(src);
     if (rc) return rc;
     if ((rc = check_device())) return rc;
     if ((rc = device_sm_count(sms))) return rc;
-    if (*sms > 1024) return fail(QUARTET_E_ARG, "more SMs than the probe's host buffer holds");
+    if (*sms > PROBE_MAX_SMS) return fail(QUARTET_E_ARG, "more SMs than the probe's host buffer holds");
     return QUARTET_OK;
 }
 
@@ -113,9 +124,19 @@ extern "C" __attribute__((visibility("default"))) int quartet_probe_copy_ingress
                      static_cast<cudaStream_t>(stream));
 }
 
-// The same measurement without any workspace from the caller and without allocating: the per-SM cycle
-// counts go to the file-scope device array above, whose address is looked up once per device.  A device
-// with more SMs than the array holds is rejected.
+// The same measurement for callers that must not allocate device memory while they run: code inside a
+// region where the framework's caching allocator is frozen (a memory-pool snapshot, a stream capture in
+// progress elsewhere in the process), a plugin that was handed fixed buffers by its host application, or
+// a monitoring hook that runs when the device is nearly full and a cudaMalloc would fail or synchronise.
+// The kernel's scratch (one cycle count per SM) is the file-scope device array above instead of a caller
+// workspace; this call and everything below it call no cudaMalloc / cudaFree and no allocating library.
+//   * Limit: devices with more than 256 SMs are rejected with QUARTET_E_ARG.
+//   * Set-up: the FIRST call of a thread on a device looks up the array's device address
+//     (cudaGetSymbolAddress, checked) with that device current and keeps it; make that first call
+//     before any stream capture begins.
+//   * Sharing: every call on a device writes the same array (the kernel overwrites all entries it reads
+//     back, so nothing needs clearing), and the array keeps the last call's counts.  Calls that overlap
+//     on the GPU -- two streams, two host threads -- race on it; the caller serialises them.
 extern "C" __attribute__((visibility("default"))) int quartet_probe_copy_ingress_noalloc(const void* src, uint64_t region, int32_t iters,
                                                                                          int32_t stages, int32_t chunk, int32_t producers,
                                                                                          double* bytes_per_clk_per_sm, quartet_stream_t stream) {

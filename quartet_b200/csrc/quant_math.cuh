@@ -148,7 +148,7 @@ __device__ __forceinline__ float pow2_biased(int b) { return __uint_as_float((ui
 // ---------------------------------------------------------------------------
 // Eight values -> eight e2m1 codes in one word (element 0 in the lowest nibble) with the hardware
 // round-to-nearest-even conversion.  Differs from the reference's strict-`>` ladder
-// (mxfp4_triton.py:131-159) only when |v| is EXACTLY 0.75, 1.75 or 3.5.
+// (mxfp4_triton.py:131-159) only when |v| is EXACTLY 0.75, 1.75 or 3.5; cvt_e2m1x8_ties_down repairs those.
 __device__ __forceinline__ uint32_t cvt_e2m1x8_rn(const float* v) {
     uint32_t r;
     asm("{\n\t.reg .b8 b0, b1, b2, b3;\n\t.reg .b16 h0, h1;\n\t"
@@ -196,6 +196,26 @@ __device__ __forceinline__ int sr_index_exact(float a, float u) {
 __device__ __forceinline__ uint32_t cvt_rs_e2m1x4(float x0, float x1, float x2, float x3, uint32_t rbits) {
     uint16_t r;
     asm("cvt.rs.satfinite.e2m1x4.f32 %0, {%1, %2, %3, %4}, %5;" : "=h"(r) : "f"(x3), "f"(x2), "f"(x1), "f"(x0), "r"(rbits));
+    return r;
+}
+
+// Eight values -> eight e2m1 codes rounded exactly like the reference ladder (round to nearest, ties toward
+// the SMALLER magnitude: mxfp4_triton.py:131-159).  The hardware round-to-nearest-even conversion agrees
+// with the ladder everywhere except at |v| == 0.75, 1.75, 3.5, which it rounds up.  Those are found without
+// a compare per value: the stochastic-rounding conversion with the constant dither 0x7FFE in all four
+// positions (rbits 0x7F7FFEFE, see cvt_rs_e2m1x4) rounds up iff the value lies at least 2^-15 of a grid
+// step above the midpoint, so it rounds every exact tie DOWN and differs from round-to-nearest-even only
+// for values in the sliver [midpoint, midpoint + 2^-15 step) -- about one group in a thousand.  Words
+// on which the two conversions disagree are redone with the ladder itself.
+__device__ __forceinline__ uint32_t cvt_e2m1x8_ties_down(const float* v) {
+    const uint32_t rn = cvt_e2m1x8_rn(v);
+    constexpr uint32_t DITHER = 0x7F7FFEFEu;
+    const uint32_t rs = cvt_rs_e2m1x4(v[0], v[1], v[2], v[3], DITHER) | (cvt_rs_e2m1x4(v[4], v[5], v[6], v[7], DITHER) << 16);
+    if (rs == rn) return rn;
+    uint32_t r = 0;
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+        r |= ((uint32_t)rtn_index_exact(fabsf(v[i])) | ((__float_as_uint(v[i]) >> 28) & 8u)) << (4 * i);
     return r;
 }
 

@@ -121,7 +121,7 @@ __global__ void __launch_bounds__(ROWS_THREADS, F32 ? 3 : 4) quant_rows_kernel(c
 #pragma unroll
             for (int i = 0; i < 16; ++i) unpack2(mul2(pack2(w[2 * i], w[2 * i + 1]), c2), v[2 * i], v[2 * i + 1]);
 #pragma unroll
-            for (int q = 0; q < 4; ++q) words[q] = cvt_e2m1x8_rn(&v[8 * q]);
+            for (int q = 0; q < 4; ++q) words[q] = cvt_e2m1x8_ties_down(&v[8 * q]);
             // (the reference gives exact zeros a minus sign, `v > 0 ? + : -`; here +0 stays +0)
 #pragma unroll
             for (int i = 31; i >= 0; --i) {

@@ -60,3 +60,31 @@ class HostStager:
         ev = torch.cuda.Event()
         ev.record(torch.cuda.current_stream(self.device))
         self._free[key] = ev
+
+
+class HostDrain:
+    """Device -> pinned host copies of a step's results on their own stream, so that they leave over PCIe
+    while the compute stream runs the next layer.  `push` orders the copy after everything the compute
+    stream has been given so far; `join` makes the compute stream wait for all copies pushed so far."""
+
+    def __init__(self, device: torch.device):
+        if torch.device(device).type != "cuda":
+            raise RuntimeError("HostDrain copies out of CUDA memory; there is no CPU path")
+        self.device = torch.device(device)
+        self.stream = torch.cuda.Stream(device=self.device)
+        self.bytes_copied = 0
+
+    def push(self, host_tensor: torch.Tensor, device_tensor: torch.Tensor) -> None:
+        if not host_tensor.is_pinned():
+            raise ValueError("the host tensor must be pinned for the copy to be asynchronous")
+        if host_tensor.shape != device_tensor.shape or host_tensor.dtype != device_tensor.dtype:
+            raise ValueError(f"host buffer {tuple(host_tensor.shape)} {host_tensor.dtype} does not match the result "
+                             f"{tuple(device_tensor.shape)} {device_tensor.dtype}")
+        self.stream.wait_stream(torch.cuda.current_stream(self.device))
+        with torch.cuda.stream(self.stream):
+            host_tensor.copy_(device_tensor, non_blocking=True)
+        device_tensor.record_stream(self.stream)
+        self.bytes_copied += host_tensor.numel() * host_tensor.element_size()
+
+    def join(self) -> None:
+        torch.cuda.current_stream(self.device).wait_stream(self.stream)
