@@ -51,7 +51,35 @@ def make_input(rows, cols, dtype, gauss=False, seed=0):
     return x.to(dtype)
 
 
+GRAPH_LAUNCHES = 0  # --graph N: time N back-to-back launches replayed from a CUDA graph (no host work between kernels)
+
+
+def time_graph(fn, iters, warmup, n):
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        for _ in range(n):
+            fn()
+    g.replay()
+    torch.cuda.synchronize()
+    best, total = float("inf"), 0.0
+    for _ in range(iters):
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        g.replay()
+        e.record()
+        e.synchronize()
+        ms = s.elapsed_time(e) / n
+        total += ms
+        best = min(best, ms)
+    return total / iters, best
+
+
 def time_kernel(fn, iters, warmup, flush=True):
+    if GRAPH_LAUNCHES:
+        return time_graph(fn, iters, warmup, GRAPH_LAUNCHES)
     scratch = torch.empty(256 << 20, dtype=torch.uint8, device="cuda") if flush else None
     for _ in range(warmup):
         fn()
@@ -72,7 +100,7 @@ def time_kernel(fn, iters, warmup, flush=True):
     return total / iters, best
 
 
-def run_quant(kernel, rows, cols, dtype, rounding, iters, warmup, gauss):
+def run_quant(kernel, rows, cols, dtype, rounding, iters, warmup, gauss, flush=True):
     esz = 2 if dtype == torch.bfloat16 else 4
     if kernel == "requant_t":
         x = make_input(rows, cols, torch.bfloat16, gauss)
@@ -91,15 +119,15 @@ def run_quant(kernel, rows, cols, dtype, rounding, iters, warmup, gauss):
         else:
             fn = lambda: ops.quant_bwd_t(x, rounding=rounding, seed=1)  # noqa: E731
         bytes_ = rows * cols * (esz + BYTES_PER_ELEM[kernel])
-    avg, best = time_kernel(fn, iters, warmup)
+    avg, best = time_kernel(fn, iters, warmup, flush)
     hbm = _peaks().get("hbm_gbs", 6650.0)
     gbs = bytes_ / (avg * 1e-3) / 1e9
-    return {"kernel": kernel, "rows": rows, "cols": cols, "dtype": "bf16" if esz == 2 else "f32", "rounding": rounding,
+    return {"kernel": kernel, "rows": rows, "cols": cols, "dtype": "bf16" if esz == 2 else "f32", "rounding": rounding, "l2_flushed_between_launches": bool(flush),
             "avg_ms": round(avg, 4), "best_ms": round(best, 4), "GB/s": round(gbs, 1), "frac_of_hbm_peak": round(gbs / hbm, 4),
             "algorithmic_bytes": int(bytes_)}
 
 
-def run_gemm(m, n, k, iters, warmup, fused, out_f32):
+def run_gemm(m, n, k, iters, warmup, fused, out_f32, flush=True):
     g = torch.Generator(device="cuda").manual_seed(0)
     a = torch.randint(0, 256, (m, k // 2), generator=g, device="cuda", dtype=torch.uint8)
     b = torch.randint(0, 256, (n, k // 2), generator=g, device="cuda", dtype=torch.uint8)
@@ -108,12 +136,12 @@ def run_gemm(m, n, k, iters, warmup, fused, out_f32):
     mask = torch.randint(0, 256, (m, n // 8), generator=g, device="cuda", dtype=torch.uint8) if fused else None
     out = torch.empty(m, n, device="cuda", dtype=torch.float32 if out_f32 else torch.bfloat16)
     fn = lambda: ops.gemm_mxfp4_tn(a, asf, b, bsf, 16 / 9, mask=mask, out=out)  # noqa: E731
-    avg, best = time_kernel(fn, iters, warmup)
+    avg, best = time_kernel(fn, iters, warmup, flush)
     p = _peaks()
     peak = 4 * p.get("bf16_tflops", 1590.0)
     tf = 2.0 * m * n * k / (avg * 1e-3) / 1e12
     return {"kernel": "gemm_mxfp4_tn", "m": m, "n": n, "k": k, "fused_unrotate": bool(fused), "out": "f32" if out_f32 else "bf16",
-            "avg_ms": round(avg, 4), "best_ms": round(best, 4), "TFLOP/s": round(tf, 1),
+            "l2_flushed_between_launches": bool(flush), "avg_ms": round(avg, 4), "best_ms": round(best, 4), "TFLOP/s": round(tf, 1),
             "frac_of_4x_bf16_burst_peak": round(tf / peak, 4)}
 
 
@@ -132,8 +160,12 @@ def main():
     ap.add_argument("--gauss", action="store_true")
     ap.add_argument("--fused-unrotate", action="store_true")
     ap.add_argument("--out-f32", action="store_true")
+    ap.add_argument("--no-flush", action="store_true", help="do not flush L2 between launches (operands of the previous launch stay cached)")
+    ap.add_argument("--graph", type=int, default=0, help="time N back-to-back launches replayed from a CUDA graph instead of single launches")
     ap.add_argument("--sweep", action="store_true", help="quantize-only sweep: K in {4096, 8192, 14336}, M = 4096 .. 131072")
     args = ap.parse_args()
+    global GRAPH_LAUNCHES
+    GRAPH_LAUNCHES = args.graph
     dtype = torch.bfloat16 if args.dtype == "bf16" else torch.float32
     if args.sweep:
         for k in (4096, 8192, 14336):
@@ -152,9 +184,9 @@ def main():
                               "bytes_per_clk_per_sm": round(v, 1)}), flush=True)
         return
     if args.kernel == "gemm":
-        print(json.dumps(run_gemm(args.m, args.n, args.k, args.iters, args.warmup, args.fused_unrotate, args.out_f32)))
+        print(json.dumps(run_gemm(args.m, args.n, args.k, args.iters, args.warmup, args.fused_unrotate, args.out_f32, not args.no_flush)))
     else:
-        print(json.dumps(run_quant(args.kernel, args.rows, args.cols, dtype, args.rounding, args.iters, args.warmup, args.gauss)))
+        print(json.dumps(run_quant(args.kernel, args.rows, args.cols, dtype, args.rounding, args.iters, args.warmup, args.gauss, not args.no_flush)))
 
 
 if __name__ == "__main__":

@@ -117,23 +117,29 @@ __global__ void __launch_bounds__(ROWS_THREADS, F32 ? 3 : 4) quant_rows_kernel(c
             e8m0 = exp_field(scales);
             const float c = h * pow2_biased(254 - e8m0);  // h * 2^-e
             float v[32];
-            const f32x2_t c2 = pack2(c, c);
+            const f32x2_t c2 = pack2(c, c), m36 = pack2(-36.f, -36.f);
+            // mask bit = |v| < 6  <=>  v * v - 36 < 0; the fused multiply-add rounds the exact difference, so its
+            // sign is exact (and |v| == 6 gives +0: clipped, as in the reference's strict `<`)
 #pragma unroll
-            for (int i = 0; i < 16; ++i) unpack2(mul2(pack2(w[2 * i], w[2 * i + 1]), c2), v[2 * i], v[2 * i + 1]);
+            for (int i = 15; i >= 0; --i) {
+                const f32x2_t vp = mul2(pack2(w[2 * i], w[2 * i + 1]), c2);
+                unpack2(vp, v[2 * i], v[2 * i + 1]);
+                float t0, t1;
+                unpack2(fma2(vp, vp, m36), t0, t1);
+                mbits = __funnelshift_l(__float_as_uint(t1), mbits, 1);
+                mbits = __funnelshift_l(__float_as_uint(t0), mbits, 1);
+            }
 #pragma unroll
             for (int q = 0; q < 4; ++q) words[q] = cvt_e2m1x8_ties_down(&v[8 * q]);
             // (the reference gives exact zeros a minus sign, `v > 0 ? + : -`; here +0 stays +0)
-#pragma unroll
-            for (int i = 31; i >= 0; --i) {
-                const float t = fabsf(v[i]) - 6.0f;  // negative <=> |v| < 6
-                mbits = __funnelshift_l(__float_as_uint(t), mbits, 1);
-            }
         } else {
             const uint64_t g = (uint64_t)grow * (uint64_t)(p.cols >> 5) + (uint64_t)((col0 >> 5) + gk);
             const int64_t flat = grow * p.cols + col0 + gk * 32;
             absmax_quantize_group<ROUND>(w, h, g, flat, grow < p.rows, p.seed, p.offset, p.noise, flip, words, e8m0);
         }
-        *reinterpret_cast<uint4*>(s_codes + row * 64 + gk * 16) = make_uint4(words[0], words[1], words[2], words[3]);
+        // 64-byte rows, 16-byte chunk c of row r at chunk c ^ ((r >> 1) & 3): what the 64B-swizzled tensor map of
+        // the store expects; a quarter-warp's eight 16-byte stores then fall into eight different bank groups
+        *reinterpret_cast<uint4*>(s_codes + row * 64 + ((gk ^ ((row >> 1) & 3)) << 4)) = make_uint4(words[0], words[1], words[2], words[3]);
         if (KIND == KIND_QUEST) *reinterpret_cast<uint32_t*>(s_mask + row * 16 + gk * 4) = mbits;
         s_sf[(row & 31) * 16 + (row >> 5) * 4 + gk] = (uint8_t)e8m0;
     }
@@ -163,13 +169,13 @@ static int launch_rows(const void* x, const RowsParams& p, uint8_t* codes, uint8
     else
         rc = make_tmap_2d(&tm_x, x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, p.cols, p.rows, p.cols * 2, 64, box_rows, 3);
     if (rc) return rc;
-    rc = make_tmap_2d(&tm_codes, codes, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, p.cols / 2, p.rows, p.cols / 2, 64, box_rows, 0);
+    rc = make_tmap_2d(&tm_codes, codes, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, p.cols / 2, p.rows, p.cols / 2, 64, box_rows, 2);
     if (rc) return rc;
     if (mask) {
         rc = make_tmap_2d(&tm_mask, mask, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, p.cols / 8, p.rows, p.cols / 8, 16, box_rows, 0);
         if (rc) return rc;
     } else {
-        tm_mask = tm_codes;
+        tm_mask = tm_codes;  // never used: the kernel stores no mask
     }
     auto kern = quant_rows_kernel<KIND, ROUND, F32>;
     constexpr int smem = rows_smem_bytes<F32>();

@@ -147,7 +147,8 @@ __global__ void __launch_bounds__(TT_THREADS, (SRC == SRC_F32 && DUAL) ? 2 : 4)
         uint32_t words[4];
         int e8m0;
         absmax_quantize_group<ROUND>(a, p.had_scale, g, flat, true, p.seed, p.offset, p.noise, flip, words, e8m0);
-        *reinterpret_cast<uint4*>(s_codes + oc * 64 + rg * 16) = make_uint4(words[0], words[1], words[2], words[3]);
+        // 64B-swizzled staging (16-byte chunk c of row r at chunk c ^ ((r >> 1) & 3)), matching the store's tensor map
+        *reinterpret_cast<uint4*>(s_codes + oc * 64 + ((rg ^ ((oc >> 1) & 3)) << 4)) = make_uint4(words[0], words[1], words[2], words[3]);
         s_sf[(oc & 31) * 16 + (oc >> 5) * 4 + rg] = (uint8_t)e8m0;
     }
 
@@ -167,7 +168,7 @@ __global__ void __launch_bounds__(TT_THREADS, (SRC == SRC_F32 && DUAL) ? 2 : 4)
             uint32_t words[4];
             int e8m0;
             absmax_quantize_group<ROUND>(w, p.had_scale, g, flat, true, p.seed_rows, p.offset, p.noise, flip, words, e8m0);
-            *reinterpret_cast<uint4*>(s_codes_r + row * 64 + gk * 16) = make_uint4(words[0], words[1], words[2], words[3]);
+            *reinterpret_cast<uint4*>(s_codes_r + row * 64 + ((gk ^ ((row >> 1) & 3)) << 4)) = make_uint4(words[0], words[1], words[2], words[3]);
             s_sf_r[(row & 31) * 16 + (row >> 5) * 4 + gk] = (uint8_t)e8m0;
         }
     }
@@ -187,6 +188,148 @@ __global__ void __launch_bounds__(TT_THREADS, (SRC == SRC_F32 && DUAL) ? 2 : 4)
     }
 }
 
+// ---------------------------------------------------------------------------
+// MXFP4 source (quartet_requant_t): its own kernel.  The source tile is 128 rows x 64 code bytes plus one
+// 512-byte scale block.  The scales are first expanded to floats (times in_scale) in shared memory, grouped
+// as [32-row group][32-column block][row], so that a thread fetches the 32 scales of its rows with eight
+// 128-bit loads instead of 32 byte loads, shifts and multiplies.  A thread owns one source byte column (two
+// adjacent source columns) over 32 rows: every byte is loaded and decoded ONCE (cvt.rn.f16x2.e2m1x2 yields
+// both values); the second column's values wait, already scaled, as packed halves of one register per row
+// pair while the first column is rotated, rounded and packed.  Launched for in_scale == 1 only (what the
+// backward pass uses); any other in_scale takes the generic tile kernel above, with identical results.
+// ---------------------------------------------------------------------------
+constexpr int RQ_IN_BYTES = TT * 64 + 512;       // codes + scale block, as the copies deliver them
+constexpr int RQ_SCALE_FLOATS = 4 * 4 * 32;      // [row group][column block][row]
+constexpr int RQ_SMEM = RQ_IN_BYTES + RQ_SCALE_FLOATS * 4 + TT * 64 + 512 + 64 + 1024;
+
+__device__ __forceinline__ uint32_t e2m1x2_to_half2_bits(uint32_t byte) {
+    uint32_t h2;
+    asm("{\n\t.reg .b8 lo, hi;\n\t.reg .b16 t;\n\tcvt.u16.u32 t, %1;\n\tmov.b16 {lo, hi}, t;\n\t"
+        "cvt.rn.f16x2.e2m1x2 %0, lo;\n\t}"
+        : "=r"(h2)
+        : "r"(byte));
+    return h2;
+}
+
+#ifndef RQ_MIN_CTAS
+#define RQ_MIN_CTAS 4
+#endif
+template <int ROUND>
+__global__ void __launch_bounds__(TT_THREADS, RQ_MIN_CTAS)
+    requant_t_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant__ CUtensorMap tm_out, const TileTParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t* s_in = smem;                                                  // [128 rows][64 B] codes, then 512 B of scales
+    float* s_scale = reinterpret_cast<float*>(smem + RQ_IN_BYTES);         // 2 KB
+    uint8_t* s_codes = smem + RQ_IN_BYTES + RQ_SCALE_FLOATS * 4;           // [128 out rows][64 B], 64B-swizzled
+    uint8_t* s_sf = s_codes + TT * 64;                                     // 512 B
+    uint64_t* bar = reinterpret_cast<uint64_t*>(s_sf + 512);
+
+    const int tid = threadIdx.x;
+    const int col0 = blockIdx.x * TT, row0 = blockIdx.y * TT;
+    if (tid == 0) {
+        mbar_init(bar, 1);
+        fence_mbar_init();
+    }
+    __syncthreads();
+    pdl_launch_dependents();
+    pdl_wait();  // no global access before this point
+    if (tid == 0) {
+        mbar_arrive_expect_tx(bar, TT * 64 + 512);
+        tma_load_2d(s_in, &tm_in, col0 / 2, row0, bar);
+        bulk_load(s_in + TT * 64, p.sf_in + ((int64_t)blockIdx.y * p.sf_in_blocks_per_rowblock + blockIdx.x) * 512, 512, bar);
+    }
+    const uint32_t signs = p.signs_dev ? __ldg(p.signs_dev) : p.signs;
+    uint32_t flip[4];
+#pragma unroll
+    for (int q = 0; q < 4; ++q) flip[q] = spread_sign_bits((signs >> (8 * q)) & 0xFFu);
+
+    mbar_wait(bar, 0, WAIT_QUANT_LOAD);
+    {   // scale bytes -> floats: source byte (r % 32) * 16 + (r / 32) * 4 + kb  ->  s_scale[((r / 32) * 4 + kb) * 32 + r % 32]
+        const uint8_t* s_sfin = s_in + TT * 64;
+        const uint32_t two = *reinterpret_cast<const uint16_t*>(s_sfin + 2 * tid);
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+            const int b = 2 * tid + j;
+            const int i = b >> 4, rgq = (b >> 2) & 3, kb = b & 3;
+            s_scale[(rgq * 4 + kb) * 32 + i] = __uint_as_float(((two >> (8 * j)) & 0xFFu) << 23) * p.in_scale;
+        }
+    }
+    __syncthreads();
+
+    const int cp = tid & 63;   // source byte column = source column pair
+    const int rg = tid >> 6;   // group of 32 source rows
+    const int64_t out_kb = (int64_t)(row0 >> 5) + rg;
+    const int64_t groups_per_out_row = p.rows >> 5;
+    const float4* sc4 = reinterpret_cast<const float4*>(s_scale + (rg * 4 + (cp >> 4)) * 32);
+
+    float a[32];        // the column being quantized
+    uint32_t held[16];  // the second column, rows 2j and 2j+1 as the upper halves of their fp32 patterns
+    {
+        // in_scale == 1 (the only case this kernel is launched for): a value is grid * 2^k, at most two mantissa
+        // bits, so the upper 16 bits of its fp32 pattern hold it exactly and the second column waits in 16
+        // registers instead of 32
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+            const float4 sc = sc4[q];
+            const float scv[4] = {sc.x, sc.y, sc.z, sc.w};
+#pragma unroll
+            for (int t = 0; t < 4; t += 2) {
+                const int i = 4 * q + t;
+                const uint32_t h0 = e2m1x2_to_half2_bits(s_in[(rg * 32 + i) * 64 + cp]);
+                const uint32_t h1 = e2m1x2_to_half2_bits(s_in[(rg * 32 + i + 1) * 64 + cp]);
+                const float2 f0 = __half22float2(*reinterpret_cast<const __half2*>(&h0));
+                const float2 f1 = __half22float2(*reinterpret_cast<const __half2*>(&h1));
+                a[i] = f0.x * scv[t];
+                a[i + 1] = f1.x * scv[t + 1];
+                held[i >> 1] = __byte_perm(__float_as_uint(f0.y * scv[t]), __float_as_uint(f1.y * scv[t + 1]), 0x7632);
+            }
+        }
+    }
+#pragma unroll 1
+    for (int c = 0; c < 2; ++c) {
+        if (c == 1) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+                a[2 * j] = __uint_as_float(held[j] << 16);
+                a[2 * j + 1] = __uint_as_float(held[j] & 0xFFFF0000u);
+            }
+        }
+        wht32(a);
+        const int oc = 2 * cp + c;
+        const int64_t orow = (int64_t)col0 + oc;
+        const uint64_t g = (uint64_t)orow * (uint64_t)groups_per_out_row + (uint64_t)out_kb;
+        const int64_t flat = orow * p.rows + out_kb * 32;
+        uint32_t words[4];
+        int e8m0;
+        absmax_quantize_group<ROUND>(a, p.had_scale, g, flat, true, p.seed, p.offset, p.noise, flip, words, e8m0);
+        // 64-byte rows, 16-byte chunk c of row r stored at chunk c ^ ((r >> 1) & 3): the layout the 64B-swizzled
+        // tensor map of the store expects, and conflict-free for these 16-byte stores
+        *reinterpret_cast<uint4*>(s_codes + oc * 64 + ((rg ^ ((oc >> 1) & 3)) << 4)) = make_uint4(words[0], words[1], words[2], words[3]);
+        s_sf[(oc & 31) * 16 + (oc >> 5) * 4 + rg] = (uint8_t)e8m0;
+    }
+    fence_proxy_async_smem();
+    __syncthreads();
+    if (tid == 0) {
+        tma_store_2d(&tm_out, row0 / 2, col0, s_codes);
+        bulk_store(p.sf_t + ((int64_t)blockIdx.x * p.sf_t_blocks_per_rowblock + blockIdx.y) * 512, s_sf, 512);
+        bulk_commit();
+        bulk_wait_read0();
+    }
+}
+
+template <int ROUND>
+static int launch_requant_t(const void* src, const TileTParams& p, uint8_t* codes_t, cudaStream_t stream) {
+    CUtensorMap tm_in, tm_out;
+    int rc = make_tmap_2d(&tm_in, src, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, p.cols / 2, p.rows, p.cols / 2, 64, TT, 0);
+    if (rc) return rc;
+    if ((rc = make_tmap_2d(&tm_out, codes_t, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, p.rows / 2, p.cols, p.rows / 2, 64, TT, 2))) return rc;
+    auto kern = requant_t_kernel<ROUND>;
+    if ((rc = check_cuda(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, RQ_SMEM), "cudaFuncSetAttribute"))) return rc;
+    dim3 grid((unsigned)(p.cols / TT), (unsigned)(p.rows / TT));
+    return check_cuda(launch_pdl(kern, grid, dim3(TT_THREADS), RQ_SMEM, stream, tm_in, tm_out, p), "requant_t launch");
+}
+
 template <int SRC, int ROUND, bool DUAL = false>
 static int launch_tile_t(const void* src, const TileTParams& p, uint8_t* codes_t, cudaStream_t stream, uint8_t* codes_rows = nullptr) {
     CUtensorMap tm_in, tm_out, tm_rows;
@@ -198,10 +341,10 @@ static int launch_tile_t(const void* src, const TileTParams& p, uint8_t* codes_t
     else
         rc = make_tmap_2d(&tm_in, src, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, p.cols / 2, p.rows, p.cols / 2, 64, TT, 0);
     if (rc) return rc;
-    rc = make_tmap_2d(&tm_out, codes_t, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, p.rows / 2, p.cols, p.rows / 2, 64, TT, 0);
+    rc = make_tmap_2d(&tm_out, codes_t, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, p.rows / 2, p.cols, p.rows / 2, 64, TT, 2);
     if (rc) return rc;
     tm_rows = tm_out;
-    if (DUAL && (rc = make_tmap_2d(&tm_rows, codes_rows, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, p.cols / 2, p.rows, p.cols / 2, 64, TT, 0))) return rc;
+    if (DUAL && (rc = make_tmap_2d(&tm_rows, codes_rows, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, p.cols / 2, p.rows, p.cols / 2, 64, TT, 2))) return rc;
     auto kern = quant_tile_t_kernel<SRC, ROUND, DUAL>;
     constexpr int smem = tile_smem_bytes<SRC, DUAL>();
     rc = check_cuda(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem), "cudaFuncSetAttribute");
@@ -276,7 +419,14 @@ extern "C" __attribute__((visibility("default"))) int quartet_requant_t(const ui
     p.sf_t = sf_t, p.sf_t_blocks_per_rowblock = ((rows / 32 + 3) / 4);
     p.had_scale = had_scale, p.signs = signs, p.signs_dev = signs_dev;
     p.seed = seed, p.offset = offset, p.noise = noise;
-    return dispatch_round<SRC_MXFP4>(codes, p, codes_t, rounding, static_cast<cudaStream_t>(stream));
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (in_scale != 1.0f) return dispatch_round<SRC_MXFP4>(codes, p, codes_t, rounding, s);  // general scale: the generic tile kernel
+    switch (rounding) {
+        case 0: return launch_requant_t<0>(codes, p, codes_t, s);
+        case 1: return launch_requant_t<1>(codes, p, codes_t, s);
+        case 2: return launch_requant_t<2>(codes, p, codes_t, s);
+        default: return launch_requant_t<3>(codes, p, codes_t, s);
+    }
 }
 
 // Q(E) and Q(E^T) from one read of E: codes/sf are what quartet_quant_bwd(x, ..., seed_rows) writes,
