@@ -80,6 +80,21 @@ int quartet_quant_bwd(const void* x, int x_dtype, int64_t rows, int64_t cols, fl
                       uint8_t* codes, uint8_t* sf, quartet_stream_t stream);
 
 /*
+ * The quantizers' scaling, rounding and packing WITHOUT the built-in rotation: x [rows, cols] is taken as
+ * already rotated (or as not to be rotated) and quantized in groups of 32 along `cols`.
+ * kind 0: std-based scale, round to nearest (ties toward zero), clip mask -- the quest=True branch of
+ *         mxfp4_forward_kernel after its `tl.dot` (mxfp4_triton.py:48-57,130-174), and the rotation-free
+ *         mxfp4_quant_kernel of the post-training tools (src/quarot_utils/mxfp4_quant_utils.py:24-113);
+ * kind 1: absmax scale with the rounding modes of quartet_quant_bwd (mxfp4_triton.py:58-61,70-129).
+ * Serves rotations this library has no kernel for -- a dense random orthogonal matrix (rerotate="O32",
+ * mxfp4.py:61-64) or hadamard_dim 64 / 128 (sweep_tokens_backward.sh:52-53): the caller multiplies by the
+ * matrix, this call does the rest.  Noise and the tl.rand offsets index x row-major.
+ */
+int quartet_quant_group32(const void* x, int x_dtype, int64_t rows, int64_t cols, int kind, float gaussian_scale,
+                          int rounding, uint64_t seed, uint64_t offset, const float* noise, uint8_t* codes, uint8_t* sf,
+                          uint8_t* mask, quartet_stream_t stream);
+
+/*
  * Backward quantizer of the TRANSPOSE: groups of 32 run along `rows` of x; writes
  * codes_t [cols, rows/2] and sf_t (logical [cols, rows/32]).
  * Replaces `g_quantizer(e.reshape(M,-1).T.contiguous())` (backward.py:81); contract =

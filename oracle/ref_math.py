@@ -65,8 +65,9 @@ def signs_to_diag(signs: int) -> torch.Tensor:
 
 
 def rotate(x: torch.Tensor, h: torch.Tensor) -> torch.Tensor:
-    """`x.view(-1, 32) @ H` with fp32 accumulation (mxfp4_triton.py:46-47)."""
-    return (x.to(torch.float32).reshape(-1, GROUP) @ h.to(torch.float32)).contiguous()
+    """`x.view(-1, d) @ H` with fp32 accumulation, re-grouped by 32 for the scales (mxfp4_triton.py:45-50;
+    d = hadamard_dim = H's size, 32 in the production configuration)."""
+    return (x.to(torch.float32).reshape(-1, h.shape[0]) @ h.to(torch.float32)).reshape(-1, GROUP).contiguous()
 
 
 # ----------------------------------------------------------------------------

@@ -38,7 +38,9 @@ constexpr int rows_smem_bytes() {
     return TILE_R * TILE_C * (F32 ? 4 : 2) + OUT_CODES_BYTES + OUT_MASK_BYTES + OUT_SF_BYTES + 64 + 1024;
 }
 
-template <int KIND, int ROUND, bool F32>
+// ROT = false: the 32-point rotation is skipped (the values are quantized as they are, h = 1): for tensors
+// that were rotated elsewhere with a general matrix, and for the reference's rotation-free quantizer.
+template <int KIND, int ROUND, bool F32, bool ROT>
 __global__ void __launch_bounds__(ROWS_THREADS, F32 ? 3 : 4) quant_rows_kernel(const __grid_constant__ CUtensorMap tm_x,
                                                                   const __grid_constant__ CUtensorMap tm_codes,
                                                                   const __grid_constant__ CUtensorMap tm_mask,
@@ -90,8 +92,15 @@ __global__ void __launch_bounds__(ROWS_THREADS, F32 ? 3 : 4) quant_rows_kernel(c
         load_row_group<F32>(s_in, row, gk, w);
         // statistics that do not need the rotated values: sum_j xh_j = 32 h x_0 (only row 0 of the
         // Sylvester matrix has a non-zero column sum) and sum_j xh_j^2 = 32 h^2 sum_i x_i^2 (Parseval).
-        const float x0 = w[0];
+        float x0 = w[0];
         float sumsq = 0.f;
+        if (KIND == KIND_QUEST && !ROT) {
+            // no rotation: the group's own sum takes the place of 32 h x_0 (h = 1 here, see below)
+            float s = 0.f;
+#pragma unroll
+            for (int i = 0; i < 32; ++i) s += w[i];
+            x0 = s * (1.0f / 32.0f);
+        }
         if (KIND == KIND_QUEST) {
             // two interleaved partial sums (even / odd elements) in one packed accumulator
             f32x2_t acc = pack2(0.f, 0.f);
@@ -104,14 +113,15 @@ __global__ void __launch_bounds__(ROWS_THREADS, F32 ? 3 : 4) quant_rows_kernel(c
             unpack2(acc, s_even, s_odd);
             sumsq = s_even + s_odd;
         }
-        wht32(w);
+        if (ROT) wht32(w);
 
         uint32_t words[4];
         uint32_t mbits = 0;
         int e8m0;
         if (KIND == KIND_QUEST) {
-            const float mean = h * x0;
-            const float mean_sq = (h * h) * sumsq;
+            // rotated: sum_j xh_j = 32 h x_0 and sum_j xh_j^2 = 32 h^2 sum_i x_i^2; un-rotated (h = 1): the plain moments
+            const float mean = ROT ? h * x0 : x0;
+            const float mean_sq = ROT ? (h * h) * sumsq : sumsq * (1.0f / 32.0f);
             const float var = fmaxf(mean_sq - mean * mean, 0.f);
             const float scales = p.gaussian_scale * sqrtf(var) + 1e-8f;
             e8m0 = exp_field(scales);
@@ -159,7 +169,7 @@ __global__ void __launch_bounds__(ROWS_THREADS, F32 ? 3 : 4) quant_rows_kernel(c
 // ---------------------------------------------------------------------------
 // host
 // ---------------------------------------------------------------------------
-template <int KIND, int ROUND, bool F32>
+template <int KIND, int ROUND, bool F32, bool ROT = true>
 static int launch_rows(const void* x, const RowsParams& p, uint8_t* codes, uint8_t* mask, cudaStream_t stream) {
     CUtensorMap tm_x, tm_codes, tm_mask;
     int rc;
@@ -177,7 +187,7 @@ static int launch_rows(const void* x, const RowsParams& p, uint8_t* codes, uint8
     } else {
         tm_mask = tm_codes;  // never used: the kernel stores no mask
     }
-    auto kern = quant_rows_kernel<KIND, ROUND, F32>;
+    auto kern = quant_rows_kernel<KIND, ROUND, F32, ROT>;
     constexpr int smem = rows_smem_bytes<F32>();
     rc = check_cuda(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem), "cudaFuncSetAttribute");
     if (rc) return rc;
@@ -248,5 +258,39 @@ extern "C" __attribute__((visibility("default"))) int quartet_quant_bwd(const vo
         QB(0) QB(1) QB(2) QB(3)
     }
 #undef QB
+    return fail(QUARTET_E_ARG, "unreachable");
+}
+
+// Group-of-32 scaling, rounding and packing WITHOUT the rotation: x is quantized as it is.
+extern "C" __attribute__((visibility("default"))) int quartet_quant_group32(const void* x, int x_dtype, int64_t rows, int64_t cols, int kind,
+                                     float gaussian_scale, int rounding, uint64_t seed, uint64_t offset, const float* noise,
+                                     uint8_t* codes, uint8_t* sf, uint8_t* mask, quartet_stream_t stream) {
+    int rc = validate_rows(x, x_dtype, rows, cols, codes, sf);
+    if (rc) return rc;
+    if (kind != 0 && kind != 1) return fail(QUARTET_E_ARG, "kind must be 0 (std-scaled, round to nearest, clip mask) or 1 (absmax-scaled)");
+    if (mask && !aligned16(mask)) return fail(QUARTET_E_ALIGN, "mask must be 16-byte aligned");
+    RowsParams p{};
+    p.rows = rows, p.cols = cols, p.sf = sf;
+    p.sf_blocks_per_rowblock = ((cols / 32 + 3) / 4);
+    p.had_scale = 1.0f, p.gaussian_scale = gaussian_scale;
+    p.seed = seed, p.offset = offset, p.noise = noise;
+    p.box_rows = (uint32_t)(rows < TILE_R ? rows : TILE_R);
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const bool f32 = x_dtype == QUARTET_F32;
+    if (kind == 0) {
+        p.has_mask = mask != nullptr;
+        return f32 ? launch_rows<KIND_QUEST, 0, true, false>(x, p, codes, mask, s) : launch_rows<KIND_QUEST, 0, false, false>(x, p, codes, mask, s);
+    }
+    if (rounding < 0 || rounding > 3) return fail(QUARTET_E_ARG, "rounding must be 0..3");
+    if (rounding == QUARTET_ROUND_SR_NOISE && !noise) return fail(QUARTET_E_NULL, "noise tensor required for rounding mode 2");
+    if (rounding == QUARTET_ROUND_SR_TLRAND && rows * cols > 0x7FFFFFFFLL) return fail(QUARTET_E_SHAPE, "rounding mode 3 indexes elements with 31 bits");
+#define QG(R)                                                                              \
+    case R:                                                                                \
+        return f32 ? launch_rows<KIND_ABSMAX, R, true, false>(x, p, codes, nullptr, s)     \
+                   : launch_rows<KIND_ABSMAX, R, false, false>(x, p, codes, nullptr, s);
+    switch (rounding) {
+        QG(0) QG(1) QG(2) QG(3)
+    }
+#undef QG
     return fail(QUARTET_E_ARG, "unreachable");
 }

