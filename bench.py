@@ -351,6 +351,7 @@ def gpu_arm(args):
     for i in range(len(layers)):
         stager.register(i, (xs[i], es[i]))
     pending = {"items": 0}  # how many (step, layer) items of the current timed run are still to be prefetched
+    deferred = {}           # the exchange join of the step before
 
     def prefetch_next(i):
         if pending["items"] > 0:
@@ -365,6 +366,8 @@ def gpu_arm(args):
             xs[i].grad = None
             lin.weight.grad = None
             y = lin(xs[i])
+            if i == 0:
+                join_exchange()  # of the previous step: its last layer's exchange had this layer's forward to finish under
             y.backward(es[i])
             if reducer is not None:
                 reducer.submit(lin.weight.grad)
@@ -374,8 +377,18 @@ def gpu_arm(args):
                 stager.release(i)
                 if world == 1:
                     drain.push(out_host[i][2], lin.weight.grad)
-        shards = reducer.wait() if reducer is not None else (sink.wait() if sink is not None else None)
-        if from_host and shards is not None:
+        if reducer is not None or sink is not None:
+            # a step's exchange is joined after the first forward of the NEXT step (the last step's at the end of the
+            # timed region): the last layer's rows cross NVLink under the next step's first kernels
+            deferred["join"] = reducer.wait if reducer is not None else sink.wait
+            deferred["to_host"] = from_host
+
+    def join_exchange():
+        fn = deferred.pop("join", None)
+        if fn is None:
+            return
+        shards = fn()
+        if deferred.pop("to_host", False):
             for i, dw in enumerate(shards):
                 drain.push(out_host[i][2], dw)
 
@@ -390,6 +403,7 @@ def gpu_arm(args):
             prefetch_next(0)
         for _ in range(n_steps):
             step(from_host)
+        join_exchange()  # every step's exchange completes inside the region
         if from_host:
             drain.join()  # the region ends when the last result has reached host memory
         e.record()
@@ -406,6 +420,7 @@ def gpu_arm(args):
         timing["on"] = True
         for _ in range(n_steps):
             step()
+        join_exchange()
         torch.cuda.synchronize()
         timing["on"] = False
         agg = {}
@@ -420,6 +435,7 @@ def gpu_arm(args):
     nvml_index = torch.cuda.current_device() if os.environ.get("CUDA_VISIBLE_DEVICES") is None else int(os.environ["CUDA_VISIBLE_DEVICES"].split(",")[local_rank])
     for _ in range(args.warmup):
         step()
+    join_exchange()
     sampler = ClockSampler(nvml_index).start() if rank == 0 else None
     counts["n"] = 0
     total_ms = timed(args.steps, False)

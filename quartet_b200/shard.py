@@ -79,8 +79,8 @@ class PeerWgradScatter:
 
     Attach with `layer.wgrad_sink = sink`; the layer's backward then returns no dense weight gradient
     and the averaged shard (rows [rank*N/world, (rank+1)*N/world)) is found in `layer.weight.grad_shard`
-    after `sink.wait()`.  Call `wait()` once per step: the two receive buffers of a layer alternate from
-    use to use, and that per-step join is what makes reusing one of them safe.
+    after `sink.wait()`.  Call `wait()` at least once per step: the two receive buffers of a layer alternate
+    from use to use, and a buffer is reused only after the sum of its previous contents has been issued.
     """
 
     MAX_WORLD = 8
@@ -101,9 +101,12 @@ class PeerWgradScatter:
             raise ValueError(f"at most {self.MAX_WORLD} ranks (one NVLink domain)")
         self.device = torch.device(device if device is not None else torch.cuda.current_device())
         self.stream = torch.cuda.Stream(device=self.device)
+        self.copy_streams = [torch.cuda.Stream(device=self.device) for _ in range(4)]
         self.flag = torch.zeros(1, device=self.device)
         self.plans = {}
         self.pending = []
+        self.unreduced = []   # exchanges in flight: (weight, plan, parity, event "all ranks' rows have landed")
+        self.lag = 1          # how many exchanges may stay in flight before the compute stream is made to wait for the oldest
 
     def accepts(self, rows: int, cols: int, dtype: torch.dtype) -> bool:
         return (dtype == torch.float32 and rows % 256 == 0 and cols % 256 == 0 and rows % self.world == 0
@@ -164,33 +167,63 @@ class PeerWgradScatter:
 
     def wgrad(self, weight, a, a_sf, b, b_sf, alpha, mask, had_scale):
         plan = self.prepare(weight)
+        # Exchanges of earlier layers have usually completed by now: sum their slots at full speed.  An exchange of
+        # THIS layer still in flight is joined first: a receive buffer is reused only after the sum of its previous
+        # contents has been issued on every rank (that sum precedes this layer's next completion signal).
+        self._reduce_ready(block=any(pl is plan for _, pl, _, _ in self.unreduced))
         parity = plan["uses"] & 1
         plan["uses"] += 1
         dense = None
+        main = torch.cuda.current_stream(self.device)
         if self.transport == "store":
             self.ops.gemm_mxfp4_tn_scatter(a, a_sf, b, b_sf, plan["dst"][parity], plan["rpo"], alpha, mask=mask, had_scale=had_scale)
         else:
             dense = self.ops.gemm_mxfp4_tn(a, a_sf, b, b_sf, alpha, mask=mask, had_scale=had_scale, out_dtype=torch.float32)
-        out = torch.empty(plan["rpo"], plan["cols"], dtype=torch.float32, device=self.device)
-        self.stream.wait_stream(torch.cuda.current_stream(self.device))
-        with torch.cuda.stream(self.stream):
-            if dense is not None:
-                # the DMA engines push each owner's rows while the compute stream moves on; peers are
-                # visited starting after this rank so that no two ranks target one GPU at the same time
-                slot_bytes = plan["rpo"] * plan["cols"] * 4
-                for step in range(self.world):
-                    o = (self.rank + 1 + step) % self.world
+        produced = torch.cuda.Event()
+        produced.record(main)
+        if dense is not None:
+            # the DMA engines push each owner's rows while the compute stream moves on, several copies at a time
+            # (one stream per copy engine in use); peers are visited starting after this rank so that no two ranks
+            # target one GPU at the same time
+            slot_bytes = plan["rpo"] * plan["cols"] * 4
+            for step in range(self.world):
+                o = (self.rank + 1 + step) % self.world
+                cs = self.copy_streams[step % len(self.copy_streams)]
+                cs.wait_event(produced)
+                with torch.cuda.stream(cs):
                     self.ops.peer_copy(plan["dst"][parity][o], dense.data_ptr() + o * slot_bytes, slot_bytes, self.device)
-                dense.record_stream(self.stream)
-            dist.all_reduce(self.flag, group=self.group)  # every rank's GEMM of this layer has completed
+                dense.record_stream(cs)
+            for cs in self.copy_streams:
+                self.stream.wait_stream(cs)
+        else:
+            self.stream.wait_event(produced)
+        with torch.cuda.stream(self.stream):
+            dist.all_reduce(self.flag, group=self.group)  # every rank's rows of this layer have landed everywhere
+            arrived = torch.cuda.Event()
+            arrived.record(self.stream)
+        # The slot sum runs on the COMPUTE stream, after `arrived`, when a later layer's backward (or wait()) comes
+        # by: on a side stream it would run beside the persistent GEMM, get a handful of SMs and delay the CTAs of
+        # the next GEMM launch that need them.
+        self.unreduced.append((weight, plan, parity, arrived))
+        return None
+
+    def _reduce_ready(self, block: bool = False):
+        """Sums the slots of exchanges that have completed (all of them if `block`), oldest first, on the compute stream."""
+        main = torch.cuda.current_stream(self.device)
+        while self.unreduced:
+            weight, plan, parity, arrived = self.unreduced[0]
+            if not block and len(self.unreduced) <= self.lag and not arrived.query():
+                break
+            self.unreduced.pop(0)
+            main.wait_event(arrived)
+            out = torch.empty(plan["rpo"], plan["cols"], dtype=torch.float32, device=self.device)
             self.ops.shard_reduce(plan["mine"][parity], self.world, plan["rpo"] * plan["cols"], 1.0 / self.world, out)
-        out.record_stream(self.stream)
-        weight.grad_shard = out
-        self.pending.append(out)
-        return out
+            weight.grad_shard = out
+            self.pending.append(out)
 
     def wait(self):
-        torch.cuda.current_stream(self.device).wait_stream(self.stream)
+        """Joins every exchange submitted so far; returns the owned, averaged shards in submission order."""
+        self._reduce_ready(block=True)
         out, self.pending = self.pending, []
         return out
 
