@@ -265,10 +265,15 @@ extern "C" __attribute__((visibility("default"))) int quartet_quant_bwd(const vo
 extern "C" __attribute__((visibility("default"))) int quartet_quant_group32(const void* x, int x_dtype, int64_t rows, int64_t cols, int kind,
                                      float gaussian_scale, int rounding, uint64_t seed, uint64_t offset, const float* noise,
                                      uint8_t* codes, uint8_t* sf, uint8_t* mask, quartet_stream_t stream) {
+    if (kind != 0 && kind != 1) return fail(QUARTET_E_ARG, "kind must be 0 (std-scaled, round to nearest, clip mask) or 1 (absmax-scaled)");
+    if (kind == 1) {
+        if (rounding < 0 || rounding > 3) return fail(QUARTET_E_ARG, "rounding must be 0..3");
+        if (rounding == QUARTET_ROUND_SR_NOISE && !noise) return fail(QUARTET_E_NULL, "noise tensor required for rounding mode 2");
+        if (rounding == QUARTET_ROUND_SR_TLRAND && rows * cols > 0x7FFFFFFFLL) return fail(QUARTET_E_SHAPE, "rounding mode 3 indexes elements with 31 bits");
+    }
+    if (mask && !aligned16(mask)) return fail(QUARTET_E_ALIGN, "mask must be 16-byte aligned");
     int rc = validate_rows(x, x_dtype, rows, cols, codes, sf);
     if (rc) return rc;
-    if (kind != 0 && kind != 1) return fail(QUARTET_E_ARG, "kind must be 0 (std-scaled, round to nearest, clip mask) or 1 (absmax-scaled)");
-    if (mask && !aligned16(mask)) return fail(QUARTET_E_ALIGN, "mask must be 16-byte aligned");
     RowsParams p{};
     p.rows = rows, p.cols = cols, p.sf = sf;
     p.sf_blocks_per_rowblock = ((cols / 32 + 3) / 4);
@@ -281,9 +286,6 @@ extern "C" __attribute__((visibility("default"))) int quartet_quant_group32(cons
         p.has_mask = mask != nullptr;
         return f32 ? launch_rows<KIND_QUEST, 0, true, false>(x, p, codes, mask, s) : launch_rows<KIND_QUEST, 0, false, false>(x, p, codes, mask, s);
     }
-    if (rounding < 0 || rounding > 3) return fail(QUARTET_E_ARG, "rounding must be 0..3");
-    if (rounding == QUARTET_ROUND_SR_NOISE && !noise) return fail(QUARTET_E_NULL, "noise tensor required for rounding mode 2");
-    if (rounding == QUARTET_ROUND_SR_TLRAND && rows * cols > 0x7FFFFFFFLL) return fail(QUARTET_E_SHAPE, "rounding mode 3 indexes elements with 31 bits");
 #define QG(R)                                                                              \
     case R:                                                                                \
         return f32 ? launch_rows<KIND_ABSMAX, R, true, false>(x, p, codes, nullptr, s)     \

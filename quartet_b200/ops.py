@@ -3,6 +3,7 @@ current stream; all arithmetic happens in libquartet_b200.so."""
 from __future__ import annotations
 
 import ctypes as C
+import os
 
 import torch
 
@@ -283,6 +284,21 @@ def device_status() -> int:
     st = C.c_int32(0)
     _lib.check(_lib.load().quartet_device_status(C.byref(st)), "quartet_device_status")
     return st.value
+
+
+# Every wait inside the kernels is bounded: a kernel that gives up leaves its tiles unwritten and records the
+# fact in the fault word instead of hanging.  Nothing reads that word on the hot path (it costs a device
+# synchronisation), so a caller that wants wrong results turned into an exception either polls device_status()
+# itself at a point where it synchronises anyway, or sets QUARTET_CHECK_FAULTS=1: the layer's backward and
+# the gradient exchange's wait() then check the word and raise.
+CHECK_FAULTS = os.environ.get("QUARTET_CHECK_FAULTS", "0") not in ("", "0")
+
+
+def raise_on_fault(where: str) -> None:
+    if CHECK_FAULTS:
+        word = device_status()
+        if word:
+            raise _lib.QuartetError(f"{where}: a kernel gave up on a bounded wait (fault word {word:#x}); its results are incomplete")
 
 
 def unpack_mask(mask_u8: torch.Tensor) -> torch.Tensor:

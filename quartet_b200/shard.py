@@ -224,6 +224,7 @@ class PeerWgradScatter:
     def wait(self):
         """Joins every exchange submitted so far; returns the owned, averaged shards in submission order."""
         self._reduce_ready(block=True)
+        self.ops.raise_on_fault("weight-gradient exchange")  # only with QUARTET_CHECK_FAULTS=1
         out, self.pending = self.pending, []
         return out
 

@@ -242,6 +242,7 @@ def linear_bwd(e: Tensor, xc: Tensor, xs: Tensor, xm: Tensor, wc: Tensor, ws: Te
         dx = e.new_empty((0,), dtype=x_dtype)
     if dw is None:
         dw = e.new_empty((0,), dtype=w_dtype)
+    ops.raise_on_fault("QuantizedLinear backward")  # only with QUARTET_CHECK_FAULTS=1
     return dx, dw
 
 

@@ -50,6 +50,9 @@ def test_rejections(lib):
     assert lib.quartet_gemm_mxfp4_tn(p, p, p, p, 128, 128, 64, 1.0, None, 0.17, p, 0, None) == -2
     # bad enums
     assert lib.quartet_quant_fwd(p, 7, 128, 128, 0.17, 0.5, p, p, None, None) == -4
+    assert lib.quartet_quant_group32(p, 0, 128, 128, 2, 0.5, 0, 0, 0, None, p, p, None, None) == -4   # kind
+    assert lib.quartet_quant_group32(p, 0, 128, 128, 1, 0.5, 2, 0, 0, None, p, p, None, None) == -1   # noise mode without a noise tensor
+    assert lib.quartet_quant_group32(p, 0, 128, 100, 0, 0.5, 0, 0, 0, None, p, p, None, None) == -2
     # misaligned pointer
     q = C.c_void_p(p.value + 4)
     assert lib.quartet_dequant(q, p, 1, 32, 1.0, p, 1, None) == -3
