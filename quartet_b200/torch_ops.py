@@ -260,9 +260,12 @@ def _linear_setup(ctx, inputs, output):
     _, xc, xs, xm, wc, ws, wm = output
     ctx.save_for_backward(xc, xs, xm, wc, ws, wm)
     ctx.handle, ctx.x_shape, ctx.x_dtype, ctx.w_dtype = handle, x.shape, x.dtype, w.dtype
+    ctx.set_materialize_grads(False)  # the six packed outputs never receive a gradient: no zero tensors for them
 
 
 def _linear_backward(ctx, e, *unused):
+    if e is None:
+        return None, None, None, None
     xc, xs, xm, wc, ws, wm = ctx.saved_tensors
     need_dx, need_dw = ctx.needs_input_grad[0], ctx.needs_input_grad[1]
     dx, dw = torch.ops.quartet_b200.linear_bwd(e.contiguous(), xc, xs, xm, wc, ws, wm, ctx.handle, ctx.x_dtype, ctx.w_dtype, need_dx, need_dw)
