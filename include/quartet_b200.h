@@ -149,6 +149,14 @@ int quartet_unrotate_mask(const void* g, int g_dtype, const uint8_t* mask, int64
                           void* out, int out_dtype, quartet_stream_t stream);
 
 /*
+ * Sign re-randomisation of the backward rotation, H <- H @ diag(2 * draw - 1) (AlbertTsengQuantizer.re_randomize
+ * with rerotate="signs", mxfp4.py:52-60), on the device-resident sign word the quantizers read through
+ * `signs_dev`: draw is the device tensor of 32 zeros / ones the reference's torch.randint call produces (bf16 or
+ * fp32), bit j of *word is flipped where draw[j] == 0.  One launch, no host synchronisation.
+ */
+int quartet_fold_signs(const void* draw, int draw_dtype, uint32_t* word, quartet_stream_t stream);
+
+/*
  * codes + scales -> values (still in the rotated basis), out = grid[code] * 2^(sf-127) * scale.
  * Gives the tensor the reference kernel stores (mxfp4_triton.py:168-174); used by the
  * pseudo-quantizing wrapper mxfp4_forward_kernel_wrapper (mxfp4_triton.py:177-220).

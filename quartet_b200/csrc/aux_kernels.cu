@@ -82,6 +82,16 @@ __global__ void __launch_bounds__(256) unrotate_mask_kernel(const void* __restri
     store_group<F32OUT>(out, g * 32, v);
 }
 
+// One warp: lane j reads draw[j] (0 or 1; the reference turns it into the sign 2 * draw - 1), and the word of
+// negated columns (bit j set <=> sign -1 <=> draw 0) is XOR-ed into *word: H <- H @ diag(s) on the sign word.
+template <bool F32>
+__global__ void fold_signs_kernel(const void* __restrict__ draw, uint32_t* __restrict__ word) {
+    const int lane = threadIdx.x;
+    const float v = F32 ? static_cast<const float*>(draw)[lane] : __bfloat162float(static_cast<const __nv_bfloat16*>(draw)[lane]);
+    const uint32_t neg = __ballot_sync(0xFFFFFFFFu, v == 0.f);
+    if (lane == 0) *word ^= neg;
+}
+
 QUARTET_DEFINE_STATUS_READER(status_aux)
 
 }  // namespace quartet
@@ -129,4 +139,19 @@ extern "C" __attribute__((visibility("default"))) int quartet_unrotate_mask(cons
     else
         unrotate_mask_kernel<false, false><<<blocks, 256, 0, s>>>(g, mask, groups, had_scale, out);
     return check_cuda(cudaGetLastError(), "unrotate_mask launch");
+}
+
+extern "C" __attribute__((visibility("default"))) int quartet_fold_signs(const void* draw, int draw_dtype, uint32_t* word, quartet_stream_t stream) {
+    if (!draw || !word) return fail(QUARTET_E_NULL, "draw and word must be non-NULL");
+    if (draw_dtype != QUARTET_BF16 && draw_dtype != QUARTET_F32) return fail(QUARTET_E_ARG, "draw_dtype must be 0 (bf16) or 1 (f32)");
+    if (reinterpret_cast<uintptr_t>(word) & 3) return fail(QUARTET_E_ALIGN, "word must be 4-byte aligned");
+    int rc = bind_context_of(word);
+    if (rc) return rc;
+    if ((rc = check_device())) return rc;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (draw_dtype == QUARTET_F32)
+        fold_signs_kernel<true><<<1, 32, 0, s>>>(draw, word);
+    else
+        fold_signs_kernel<false><<<1, 32, 0, s>>>(draw, word);
+    return check_cuda(cudaGetLastError(), "fold_signs launch");
 }

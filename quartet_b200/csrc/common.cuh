@@ -33,6 +33,18 @@ int status_gemm(int32_t* out);
 int status_aux(int32_t* out);
 int status_probe(int32_t* out);
 
+// cudaFuncSetAttribute(MaxDynamicSharedMemorySize) once per kernel instantiation, thread and device instead of
+// before every launch.  `state` is a thread_local int of the calling (template) function, initialised to -1.
+template <typename K>
+static inline int set_max_smem_once(K kernel, int bytes, int& state) {
+    int dev = 0;
+    int rc = check_cuda(cudaGetDevice(&dev), "cudaGetDevice");
+    if (rc || state == dev) return rc;
+    if ((rc = check_cuda(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes), "cudaFuncSetAttribute"))) return rc;
+    state = dev;
+    return QUARTET_OK;
+}
+
 static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 // ---------------------------------------------------------------------------

@@ -899,7 +899,8 @@ static int launch_gemm_2cta(const uint8_t* a, const uint8_t* b, void* d, const G
                            (uint64_t)p.k_chunks * 512, 256, BN / 128, 0)))
         return rc;
     auto kern = gemm_mxfp4_2cta_kernel<BN, NSTG>;
-    rc = check_cuda(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM), "cudaFuncSetAttribute");
+    static thread_local int smem_set = -1;
+    rc = set_max_smem_once(kern, C::SMEM, smem_set);
     if (rc) return rc;
     int dev = 0, sms = 0;
     if ((rc = check_cuda(cudaGetDevice(&dev), "cudaGetDevice"))) return rc;
@@ -944,7 +945,8 @@ static int launch_gemm(const uint8_t* a, const uint8_t* b, void* d, const GemmPa
         rc = make_tmap_2d(&tm_d, d, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, p.N, p.M, (uint64_t)p.N * 2, 32, 32, 2);
     if (rc) return rc;
     auto kern = gemm_mxfp4_kernel<BN>;
-    rc = check_cuda(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM), "cudaFuncSetAttribute");
+    static thread_local int smem_set = -1;
+    rc = set_max_smem_once(kern, C::SMEM, smem_set);
     if (rc) return rc;
     int dev = 0, sms = 0;
     if ((rc = check_cuda(cudaGetDevice(&dev), "cudaGetDevice"))) return rc;

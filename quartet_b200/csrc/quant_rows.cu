@@ -189,7 +189,8 @@ static int launch_rows(const void* x, const RowsParams& p, uint8_t* codes, uint8
     }
     auto kern = quant_rows_kernel<KIND, ROUND, F32, ROT>;
     constexpr int smem = rows_smem_bytes<F32>();
-    rc = check_cuda(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem), "cudaFuncSetAttribute");
+    static thread_local int smem_set = -1;
+    rc = set_max_smem_once(kern, smem, smem_set);
     if (rc) return rc;
     dim3 grid((unsigned)(p.cols / TILE_C), (unsigned)((p.rows + TILE_R - 1) / TILE_R));
     return check_cuda(launch_pdl(kern, grid, dim3(ROWS_THREADS), smem, stream, tm_x, tm_codes, tm_mask, p), "quant_rows launch");

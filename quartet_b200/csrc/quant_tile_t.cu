@@ -325,7 +325,8 @@ static int launch_requant_t(const void* src, const TileTParams& p, uint8_t* code
     if (rc) return rc;
     if ((rc = make_tmap_2d(&tm_out, codes_t, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, p.rows / 2, p.cols, p.rows / 2, 64, TT, 2))) return rc;
     auto kern = requant_t_kernel<ROUND>;
-    if ((rc = check_cuda(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, RQ_SMEM), "cudaFuncSetAttribute"))) return rc;
+    static thread_local int smem_set = -1;
+    if ((rc = set_max_smem_once(kern, RQ_SMEM, smem_set))) return rc;
     dim3 grid((unsigned)(p.cols / TT), (unsigned)(p.rows / TT));
     return check_cuda(launch_pdl(kern, grid, dim3(TT_THREADS), RQ_SMEM, stream, tm_in, tm_out, p), "requant_t launch");
 }
@@ -347,7 +348,8 @@ static int launch_tile_t(const void* src, const TileTParams& p, uint8_t* codes_t
     if (DUAL && (rc = make_tmap_2d(&tm_rows, codes_rows, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, p.cols / 2, p.rows, p.cols / 2, 64, TT, 2))) return rc;
     auto kern = quant_tile_t_kernel<SRC, ROUND, DUAL>;
     constexpr int smem = tile_smem_bytes<SRC, DUAL>();
-    rc = check_cuda(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem), "cudaFuncSetAttribute");
+    static thread_local int smem_set = -1;
+    rc = set_max_smem_once(kern, smem, smem_set);
     if (rc) return rc;
     dim3 grid((unsigned)(p.cols / TT), (unsigned)(p.rows / TT));
     return check_cuda(launch_pdl(kern, grid, dim3(TT_THREADS), smem, stream, tm_in, tm_out, tm_rows, p), "quant_tile_t launch");

@@ -41,6 +41,25 @@ def _stream():
     return C.c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
+class _NoSwitch:
+    def __enter__(self):
+        return None
+
+    def __exit__(self, *a):
+        return False
+
+
+_NO_SWITCH = _NoSwitch()
+
+
+def _on(device):
+    """Context that makes `device` current for the call; free when it already is (the one-process-per-GPU case)."""
+    idx = device.index
+    if idx is None or idx == torch.cuda.current_device():
+        return _NO_SWITCH
+    return torch.cuda.device(device)
+
+
 def _need_cuda(*ts):
     for t in ts:
         if t is not None and not t.is_cuda:
@@ -60,7 +79,7 @@ def quant_fwd(x, had_scale=HAD_SCALE_BF16, gaussian_scale=QUEST_GAUSSIAN_SCALE, 
     codes = torch.empty(rows, cols // 2, dtype=torch.uint8, device=x.device)
     sf = torch.empty(sf_bytes(rows, cols), dtype=torch.uint8, device=x.device)
     mask = torch.empty(rows, cols // 8, dtype=torch.uint8, device=x.device) if return_mask else None
-    with torch.cuda.device(x.device):
+    with _on(x.device):
         rc = _lib.load().quartet_quant_fwd(_ptr(x), _dt(x), rows, cols, had_scale, gaussian_scale, _ptr(codes), _ptr(sf),
                                            _ptr(mask), _stream())
     _lib.check(rc, "quartet_quant_fwd")
@@ -78,7 +97,7 @@ def quant_bwd(x, had_scale=HAD_SCALE_BF16, signs=0, signs_dev=None, rounding=ROU
     codes = torch.empty(rows, cols // 2, dtype=torch.uint8, device=x.device)
     sf = torch.empty(sf_bytes(rows, cols), dtype=torch.uint8, device=x.device)
     (s, sd), (sd_, off, nz) = _sr_args(signs, signs_dev, seed, offset, noise)
-    with torch.cuda.device(x.device):
+    with _on(x.device):
         rc = _lib.load().quartet_quant_bwd(_ptr(x), _dt(x), rows, cols, had_scale, s, sd, rounding, sd_, off, nz, _ptr(codes),
                                            _ptr(sf), _stream())
     _lib.check(rc, "quartet_quant_bwd")
@@ -94,7 +113,7 @@ def quant_group32(x, kind, gaussian_scale=QUEST_GAUSSIAN_SCALE, rounding=ROUND_N
     sf = torch.empty(sf_bytes(rows, cols), dtype=torch.uint8, device=x.device)
     mask = torch.empty(rows, cols // 8, dtype=torch.uint8, device=x.device) if (kind == 0 and return_mask) else None
     m64 = 2**64 - 1
-    with torch.cuda.device(x.device):
+    with _on(x.device):
         rc = _lib.load().quartet_quant_group32(_ptr(x), _dt(x), rows, cols, kind, gaussian_scale, rounding, int(seed) & m64, int(offset) & m64,
                                                _ptr(noise), _ptr(codes), _ptr(sf), _ptr(mask), _stream())
     _lib.check(rc, "quartet_quant_group32")
@@ -108,7 +127,7 @@ def quant_bwd_t(x, had_scale=HAD_SCALE_BF16, signs=0, signs_dev=None, rounding=R
     codes_t = torch.empty(cols, rows // 2, dtype=torch.uint8, device=x.device)
     sf_t = torch.empty(sf_bytes(cols, rows), dtype=torch.uint8, device=x.device)
     (s, sd), (sd_, off, nz) = _sr_args(signs, signs_dev, seed, offset, noise)
-    with torch.cuda.device(x.device):
+    with _on(x.device):
         rc = _lib.load().quartet_quant_bwd_t(_ptr(x), _dt(x), rows, cols, had_scale, s, sd, rounding, sd_, off, nz,
                                              _ptr(codes_t), _ptr(sf_t), _stream())
     _lib.check(rc, "quartet_quant_bwd_t")
@@ -125,7 +144,7 @@ def quant_bwd_dual(x, had_scale=HAD_SCALE_BF16, signs=0, signs_dev=None, roundin
     codes_t = torch.empty(cols, rows // 2, dtype=torch.uint8, device=x.device)
     sf_t = torch.empty(sf_bytes(cols, rows), dtype=torch.uint8, device=x.device)
     m64 = 2**64 - 1
-    with torch.cuda.device(x.device):
+    with _on(x.device):
         rc = _lib.load().quartet_quant_bwd_dual(_ptr(x), _dt(x), rows, cols, had_scale, int(signs) & 0xFFFFFFFF, _ptr(signs_dev), rounding,
                                                 int(seed_rows) & m64, int(seed_t) & m64, int(offset) & m64, _ptr(codes), _ptr(sf),
                                                 _ptr(codes_t), _ptr(sf_t), _stream())
@@ -141,7 +160,7 @@ def requant_t(codes, sf, in_scale=1.0, had_scale=HAD_SCALE_BF16, signs=0, signs_
     codes_t = torch.empty(cols, rows // 2, dtype=torch.uint8, device=codes.device)
     sf_t = torch.empty(sf_bytes(cols, rows), dtype=torch.uint8, device=codes.device)
     (s, sd), (sd_, off, nz) = _sr_args(signs, signs_dev, seed, offset, noise)
-    with torch.cuda.device(codes.device):
+    with _on(codes.device):
         rc = _lib.load().quartet_requant_t(_ptr(codes), _ptr(sf), rows, cols, in_scale, had_scale, s, sd, rounding, sd_, off,
                                            nz, _ptr(codes_t), _ptr(sf_t), _stream())
     _lib.check(rc, "quartet_requant_t")
@@ -157,7 +176,7 @@ def gemm_mxfp4_tn(a, a_sf, b, b_sf, alpha=1.0, mask=None, had_scale=HAD_SCALE_BF
         raise ValueError(f"contraction extents differ: {K} vs {b.shape[1] * 2}")
     if out is None:
         out = torch.empty(M, N, dtype=out_dtype, device=a.device)
-    with torch.cuda.device(a.device):
+    with _on(a.device):
         rc = _lib.load().quartet_gemm_mxfp4_tn(_ptr(a), _ptr(a_sf), _ptr(b), _ptr(b_sf), M, N, K, alpha, _ptr(mask), had_scale,
                                                _ptr(out), _out_dt(out.dtype), _stream())
     _lib.check(rc, "quartet_gemm_mxfp4_tn")
@@ -175,7 +194,7 @@ def gemm_mxfp4_tn_scatter(a, a_sf, b, b_sf, owner_ptrs, rows_per_owner, alpha=1.
     if b.shape[1] * 2 != K:
         raise ValueError(f"contraction extents differ: {K} vs {b.shape[1] * 2}")
     arr = (C.c_void_p * len(owner_ptrs))(*[int(x) for x in owner_ptrs])
-    with torch.cuda.device(a.device):
+    with _on(a.device):
         rc = _lib.load().quartet_gemm_mxfp4_tn_scatter(_ptr(a), _ptr(a_sf), _ptr(b), _ptr(b_sf), M, N, K, alpha, _ptr(mask), had_scale,
                                                        C.cast(arr, C.c_void_p), len(owner_ptrs), rows_per_owner, _stream())
     _lib.check(rc, "quartet_gemm_mxfp4_tn_scatter")
@@ -186,7 +205,7 @@ def shard_reduce(slots_ptr, n_slots, slot_elems, scale, out):
     _need_cuda(out)
     if out.dtype != torch.float32 or not out.is_contiguous() or out.numel() != slot_elems:
         raise ValueError("out must be a contiguous fp32 tensor of slot_elems elements")
-    with torch.cuda.device(out.device):
+    with _on(out.device):
         rc = _lib.load().quartet_shard_reduce(int(slots_ptr), n_slots, slot_elems, scale, _ptr(out), _stream())
     _lib.check(rc, "quartet_shard_reduce")
     return out
@@ -255,13 +274,25 @@ def probe_copy_ingress_noalloc(src, iters=4000, stages=6, chunk=16384, producers
     return out.value
 
 
+def fold_signs(draw, word):
+    """word (int64[1] or int32[1] device tensor, low 32 bits used) ^= bits j where draw[j] == 0; draw = the 32 zeros / ones
+    of the reference's torch.randint(0, 2, (32,)) call (mxfp4.py:52-60), bf16 or fp32."""
+    _need_cuda(draw, word)
+    if draw.numel() != 32:
+        raise ValueError("draw must hold 32 values")
+    with _on(word.device):
+        rc = _lib.load().quartet_fold_signs(_ptr(draw), _dt(draw), _ptr(word), _stream())
+    _lib.check(rc, "quartet_fold_signs")
+    return word
+
+
 def unrotate_mask(g, mask=None, had_scale=HAD_SCALE_BF16, out_dtype=None):
     """((g * mask).view(-1, 32) @ H^T).view_as(g)"""
     _need_cuda(g, mask)
     out = torch.empty_like(g, dtype=out_dtype or g.dtype)
     cols = g.shape[-1]
     rows = g.numel() // cols
-    with torch.cuda.device(g.device):
+    with _on(g.device):
         rc = _lib.load().quartet_unrotate_mask(_ptr(g), _dt(g), _ptr(mask), rows, cols, had_scale, _ptr(out), _out_dt(out.dtype),
                                                _stream())
     _lib.check(rc, "quartet_unrotate_mask")
@@ -273,7 +304,7 @@ def dequant(codes, sf, scale=1.0, dtype=torch.float32):
     _need_cuda(codes, sf)
     rows, cols = codes.shape[0], codes.shape[1] * 2
     out = torch.empty(rows, cols, dtype=dtype, device=codes.device)
-    with torch.cuda.device(codes.device):
+    with _on(codes.device):
         rc = _lib.load().quartet_dequant(_ptr(codes), _ptr(sf), rows, cols, scale, _ptr(out), _out_dt(dtype), _stream())
     _lib.check(rc, "quartet_dequant")
     return out

@@ -153,9 +153,10 @@ class QuantizedLinear(nn.Linear):
             else:
                 out_dtype = x.dtype
             sink = getattr(self, "wgrad_sink", None)
-            if sink is None:
-                # one operator per direction: traceable (torch.compile) and differentiable
+            if sink is None and torch.compiler.is_compiling():
+                # one operator per direction: what torch.compile traces (and differentiates) without a graph break
                 return torch_ops.quantized_linear(x, self.weight, self._handle, out_dtype)
+            # eager: the same kernel sequence as a plain autograd function (less dispatch overhead per call)
             aq, wq = self.activation_quantizer, self.weight_quantizer
             aq._see(x)
             wq._see(self.weight)

@@ -213,14 +213,17 @@ class _Rotation(BaseQuantizer):
             self._dense = (u @ vh).to(self._h_dtype).float()
             self._signs_host, self._signs_dev = 0, None
             return
-        draw = torch.randint(0, 2, (d,), device=dev, dtype=self._h_dtype) * 2 - 1
+        draw = torch.randint(0, 2, (d,), device=dev, dtype=self._h_dtype)  # the reference's call; its signs are 2 * draw - 1
         if self._dense is not None:
-            self._dense = self._dense.to(dev) * draw.float()[None, :]
+            self._dense = self._dense.to(dev) * (draw.float() * 2 - 1)[None, :]
             return
-        bits = ((draw < 0).to(torch.int64) << torch.arange(32, device=dev, dtype=torch.int64)).sum().reshape(1)
-        if self._signs_dev is None:
-            self._signs_dev = torch.full((1,), self._signs_host, dtype=torch.int64, device=dev)
-        self._signs_dev = self._signs_dev ^ bits
+        if self._signs_dev is None or self._signs_dev.device != draw.device:
+            self._signs_dev = torch.full((1,), self._signs_host if self._signs_dev is None else self._sign_word(), dtype=torch.int64, device=dev)
+        if draw.is_cuda and draw.dtype in (torch.bfloat16, torch.float32):
+            ops.fold_signs(draw, self._signs_dev)  # one launch: pack the 32 signs and fold them into the device word
+        else:
+            bits = ((draw == 0).to(torch.int64) << torch.arange(32, device=dev, dtype=torch.int64)).sum().reshape(1)
+            self._signs_dev = self._signs_dev ^ bits
 
     def sign_args(self):
         """kwargs for the ops: the sign word either as an immediate or as a device pointer."""
