@@ -216,6 +216,13 @@ int quartet_probe_copy_ingress(const void* src, uint64_t region, int32_t iters, 
 int quartet_probe_copy_ingress_noalloc(const void* src, uint64_t region, int32_t iters, int32_t stages, int32_t chunk,
                                        int32_t producers, double* bytes_per_clk_per_sm, quartet_stream_t stream);
 
+/*
+ * Self-test of the bounded waits (no reference counterpart): one CTA waits, with a poll limit of 4096, on a barrier
+ * that nothing completes; the wait gives up, records itself in the fault word and the kernel returns normally.
+ * gave_up_dev (device int32, may be NULL) receives 1.  quartet_device_status() then reports a non-zero word.
+ */
+int quartet_selftest_wait_timeout(int32_t* gave_up_dev, quartet_stream_t stream);
+
 /* Host helpers for the blocked scale layout (`to_blocked`, benchmark_mxfp4.ipynb:1015-1016). */
 int64_t quartet_sf_offset(int64_t row, int64_t kblock, int64_t padded_kblocks);
 int64_t quartet_sf_bytes(int64_t rows, int64_t cols);

@@ -33,6 +33,7 @@ SIGNATURES = {
     "quartet_probe_copy_ingress": (_i, [_p, _u64, C.c_int32, C.c_int32, C.c_int32, C.c_int32, _p, C.POINTER(C.c_double), _p]),
     "quartet_probe_copy_ingress_noalloc": (_i, [_p, _u64, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.POINTER(C.c_double), _p]),
     "quartet_fold_signs": (_i, [_p, _i, _p, _p]),
+    "quartet_selftest_wait_timeout": (_i, [_p, _p]),
     "quartet_unrotate_mask": (_i, [_p, _i, _p, _i64, _i64, _f, _p, _i, _p]),
     "quartet_dequant": (_i, [_p, _p, _i64, _i64, _f, _p, _i, _p]),
     "quartet_sf_offset": (_i64, [_i64, _i64, _i64]),

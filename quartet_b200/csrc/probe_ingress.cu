@@ -65,6 +65,22 @@ __global__ void __launch_bounds__(PROBE_THREADS, 1)
     if (threadIdx.x == 0) cycles[blockIdx.x] = (long long)*s_elapsed;
 }
 
+// Self-test of the give-up path every kernel of the library shares: one CTA waits, with a short poll limit, on a
+// barrier that nothing will ever complete.  The wait runs out, records itself in the fault word and the kernel
+// returns normally -- no copy is in flight, no tensor memory is held, the context stays usable.
+__global__ void wait_timeout_selftest_kernel(uint32_t poll_limit, int* __restrict__ gave_up) {
+    __shared__ uint64_t bar;
+    if (threadIdx.x == 0) {
+        mbar_init(&bar, 1);
+        fence_mbar_init();
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const bool ok = mbar_wait(&bar, 0, WAIT_QUANT_LOAD, poll_limit);  // phase 0 never completes
+        if (gave_up) *gave_up = ok ? 0 : 1;
+    }
+}
+
 QUARTET_DEFINE_STATUS_READER(status_probe)
 
 }  // namespace quartet
@@ -155,4 +171,17 @@ extern "C" __attribute__((visibility("default"))) int quartet_probe_copy_ingress
         scratch = static_cast<long long*>(addr), cached_dev = dev;
     }
     return run_probe(src, region, iters, stages, chunk, producers, scratch, sms, bytes_per_clk_per_sm, static_cast<cudaStream_t>(stream));
+}
+
+// Launches the self-test above (poll limit 4096: well under a millisecond).  Afterwards quartet_device_status()
+// reports a non-zero fault word whose low byte names a load wait, and every other entry point keeps working.
+extern "C" __attribute__((visibility("default"))) int quartet_selftest_wait_timeout(int32_t* gave_up_dev, quartet_stream_t stream) {
+    if (gave_up_dev) {
+        int rc = bind_context_of(gave_up_dev);
+        if (rc) return rc;
+    }
+    int rc = check_device();
+    if (rc) return rc;
+    wait_timeout_selftest_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(4096u, gave_up_dev);
+    return check_cuda(cudaGetLastError(), "self-test launch");
 }

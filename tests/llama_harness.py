@@ -34,7 +34,7 @@ def rotary(q, k):
 
 
 class Block(nn.Module):
-    def __init__(self, Q, d, n_head, hidden, gkw, n_kv_head=None):
+    def __init__(self, Q, d, n_head, hidden, gkw, n_kv_head=None, eps=1e-6):
         super().__init__()
 
         def lin(i, o):
@@ -50,7 +50,7 @@ class Block(nn.Module):
         # grouped-query attention when n_kv_head < n_head (the Llama-3 shape: qkv is d + 2 d n_kv/n_head wide)
         self.n_kv_head = n_kv_head or n_head
         self.kv_dim = d // n_head * self.n_kv_head
-        self.ln1, self.ln2 = RMSNorm(d), RMSNorm(d)
+        self.ln1, self.ln2 = RMSNorm(d, eps), RMSNorm(d, eps)
         self.c_attn, self.attn_proj = lin(d, d + 2 * self.kv_dim), lin(d, d)
         self.w12, self.c_proj = lin(d, 2 * hidden), lin(hidden, d)
 
@@ -69,21 +69,22 @@ class Block(nn.Module):
 
 
 class TinyLlama(nn.Module):
-    def __init__(self, Q, vocab=512, d=256, n_layer=2, n_head=2, multiple_of=128, gkw=None, n_kv_head=None):
+    def __init__(self, Q, vocab=512, d=256, n_layer=2, n_head=2, multiple_of=128, gkw=None, n_kv_head=None, eps=1e-6):
         super().__init__()
         hidden = int(2 * 4 * d / 3)
         hidden = multiple_of * ((hidden + multiple_of - 1) // multiple_of)
         self.wte = nn.Embedding(vocab, d)
-        self.blocks = nn.ModuleList(Block(Q, d, n_head, hidden, gkw or {"stochastic": True, "rerotate": "signs"}, n_kv_head)
+        self.blocks = nn.ModuleList(Block(Q, d, n_head, hidden, gkw or {"stochastic": True, "rerotate": "signs"}, n_kv_head, eps)
                                     for _ in range(n_layer))
-        self.ln_f, self.lm_head = RMSNorm(d), nn.Linear(d, vocab, bias=False)
+        self.ln_f, self.lm_head = RMSNorm(d, eps), nn.Linear(d, vocab, bias=False)
         for n_, p in self.named_parameters():
             if p.dim() == 2:
                 nn.init.normal_(p, 0.0, 0.02 / math.sqrt(2 * n_layer) if n_.endswith("c_proj.weight") else 0.02)
 
-    def forward(self, idx, targets):
+    def forward(self, idx, targets, return_logits=False):
         x = self.wte(idx)
         for blk in self.blocks:
             x = blk(x)
         logits = self.lm_head(self.ln_f(x))
-        return F.cross_entropy(logits.float().view(-1, logits.size(-1)), targets.view(-1))
+        loss = F.cross_entropy(logits.float().view(-1, logits.size(-1)), targets.view(-1))
+        return (loss, logits) if return_logits else loss

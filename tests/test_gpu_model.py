@@ -122,3 +122,58 @@ def test_reference_llama_trains_on_this_package(Q, compiled):
         for n, p in model.named_parameters():
             assert p.grad is not None and torch.isfinite(p.grad).all(), n
         assert ops.device_status() == 0
+
+
+def test_training_step_matches_the_reference_models_own_step(Q, golden_dir):
+    """tests/golden/llama_tiny_step.npz holds one fp32 training step of the REFERENCE'S OWN Llama (its model code,
+    its quantization package, its kernel under the Triton interpreter; generator: tests/golden/make_model_golden.py).
+    The harness model with the same parameters, its block linears served by this library, must reproduce the loss,
+    the logits and every parameter's gradient.  Rounding is to nearest in the gradient quantizer, so nothing is
+    random; what differs is fp32 summation order (and the quantization decisions that flips)."""
+    import os
+
+    import numpy as np
+
+    from quartet_b200 import ops
+
+    g = np.load(os.path.join(golden_dir, "llama_tiny_step.npz"))
+    model = TinyLlama(Q, vocab=256, d=128, n_layer=2, n_head=1, multiple_of=256, gkw={"stochastic": False},
+                      eps=float(g["rmsnorm_eps"])).cuda()
+    assert model.blocks[0].hidden == 512
+
+    def ref_name(n):  # harness parameter name -> the reference model's
+        n = n.replace("blocks.", "transformer.h.").replace(".ln1.", ".ln_1.").replace(".ln2.", ".ln_2.")
+        n = n.replace(".c_attn.", ".attn.c_attn.").replace(".attn_proj.", ".attn.c_proj.").replace(".w12.", ".mlp.w12.")
+        if ".c_proj." in n and ".attn." not in n:
+            n = n.replace(".c_proj.", ".mlp.c_proj.")
+        return {"wte.weight": "transformer.wte.weight", "ln_f.weight": "transformer.ln_f.weight"}.get(n, n)
+
+    with torch.no_grad():
+        for n, p in model.named_parameters():
+            bits = torch.from_numpy(g["param:" + ref_name(n)])
+            p.copy_(bits.view(torch.bfloat16).float().reshape(p.shape))
+    idx, tgt = torch.from_numpy(g["idx"]).cuda(), torch.from_numpy(g["targets"]).cuda()
+    loss, logits = model(idx, tgt, return_logits=True)  # fp32 throughout, like the golden run
+    loss.backward()
+    print("loss", loss.item(), "reference", float(g["loss"]))
+    assert abs(loss.item() - float(g["loss"])) < 1e-4
+    ref_logits = torch.from_numpy(g["logits_sample"])
+    err = ((logits[:, ::8, :].float().cpu() - ref_logits).norm() / ref_logits.norm()).item()
+    print("logits rel err", err)
+    assert err < 1e-4
+    worst = (1.0, "")
+    for n, p in model.named_parameters():
+        rn = ref_name(n)
+        gn = float(g["gnorm:" + rn])
+        row = torch.from_numpy(g["grow:" + rn])
+        mine = p.grad.float().cpu()
+        assert abs(mine.norm().item() - gn) < 2e-3 * gn, (n, mine.norm().item(), gn)
+        got_row = mine.reshape(mine.shape[0], -1)[0] if mine.dim() > 1 else mine
+        if row.norm().item() == 0.0:  # e.g. the embedding row of a token that does not occur in the batch
+            assert got_row.norm().item() == 0.0, n
+            continue
+        cos = torch.nn.functional.cosine_similarity(got_row, row, dim=0).item()
+        worst = min(worst, (cos, n))
+        assert cos > 0.9999, (n, cos)
+    print("lowest first-row cosine", worst)
+    assert ops.device_status() == 0

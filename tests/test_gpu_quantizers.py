@@ -264,3 +264,21 @@ def test_quant_bwd_dual_equals_the_two_separate_quantizers(ops, dtype, rounding)
     with pytest.raises(ValueError):
         ops.quant_bwd_dual(x[:100], ops.HAD_SCALE_BF16)  # rows not a multiple of 128
     assert ops.device_status() == 0
+
+
+def test_a_wait_that_runs_out_sets_the_fault_word_and_leaves_the_context_usable(ops):
+    """Every wait in the kernels is bounded; this drives one to its limit on purpose-built ground (a barrier nothing
+    completes, 4096 polls): the kernel returns, the fault word names the wait, is cleared by reading it, and the next
+    kernel runs normally."""
+    from quartet_b200 import _lib
+
+    assert ops.device_status() == 0
+    flag = torch.zeros(1, dtype=torch.int32, device="cuda")
+    rc = _lib.load().quartet_selftest_wait_timeout(flag.data_ptr(), torch.cuda.current_stream().cuda_stream)
+    assert rc == 0
+    word = ops.device_status()
+    assert flag.item() == 1 and word & 0x100 and (word & 0xFF) == 1  # "gave up" bit + the code of a load wait
+    assert ops.device_status() == 0                                    # reading cleared it
+    x = torch.randn(128, 128, device="cuda", dtype=torch.bfloat16)
+    codes, sf, mask = ops.quant_fwd(x)
+    assert torch.isfinite(ops.dequant(codes, sf).sum()).item() and ops.device_status() == 0
