@@ -13,8 +13,12 @@ owner's memory by the DMA engines or by the GEMM's own stores, or an NCCL reduce
 Metric: model FLOP/s = 6*M*N*K per layer, summed over layers and GPUs.
 
 Secondary workloads (same code path, their own JSON line): "quantized_linear_8192x640x2560" (one
-layer, X [8192, 640], W [2560, 640]) and "llama30m_linears_32768tok" (the 24 block linears of the
-30M model, d 640, SwiGLU 1792, at batch 64 x 512 tokens).
+layer, X [8192, 640], W [2560, 640]), "llama30m_linears_32768tok" (the 24 block linears of the
+30M model, d 640, SwiGLU 1792, at batch 64 x 512 tokens), "llama3_8b_linears_32768tok" (the four
+block linears of a Llama-3-8B layer at 8 x 4096 tokens), and "llama30m_step": a whole training step
+(forward, backward under bf16 autocast, AdamW) of a 30M Llama-style model whose block linears are
+QuantizedLinear (6 blocks, width 640, 5 heads, SwiGLU 1792, vocabulary 32000, 64 x 512 uniform-random
+token ids; the model is the test harness tests/llama_harness.py; add --compile for torch.compile).
 
 What the line reports:
   value      K steps with inputs resident in HBM, CUDA events, max over ranks
@@ -48,6 +52,8 @@ sys.path.insert(0, ROOT)
 WORKLOADS = {
     "llama7b_linears_16384tok": {"tokens": 16384, "layers": [("qkv", 4096, 12288), ("o", 4096, 4096), ("gate_up", 4096, 22016), ("down", 11008, 4096)]},
     "quantized_linear_8192x640x2560": {"tokens": 8192, "layers": [("fc", 640, 2560)]},
+    # the block linears of a Llama-3-8B layer (32 query / 8 key-value heads of 128: fused QKV is 4096 -> 6144; SwiGLU 14336) at 8 x 4096 tokens
+    "llama3_8b_linears_32768tok": {"tokens": 32768, "layers": [("qkv", 4096, 6144), ("o", 4096, 4096), ("gate_up", 4096, 28672), ("down", 14336, 4096)]},
     "llama30m_linears_32768tok": {"tokens": 32768, "layers": [(f"{name}{i}", k, n) for i in range(6) for name, k, n in
                                                                (("c_attn", 640, 1920), ("attn_proj", 640, 640), ("w12", 640, 3584), ("c_proj", 1792, 640))]},
 }
@@ -540,16 +546,72 @@ def gpu_arm(args):
         dist.destroy_process_group()
 
 
+def model_step_arm(args):
+    """One GPU, whole-model training step; prints tokens/s and the linear layers' share of it."""
+    import torch
+
+    import __graft_entry__ as entry
+
+    entry.build()
+    import quartet_b200.quantization as Q
+    from quartet_b200 import ops
+    from tests.llama_harness import TinyLlama
+
+    torch.cuda.set_device(0)
+    torch.manual_seed(0)
+    batch, seq, vocab = 64, 512, 32000
+    model = TinyLlama(Q, vocab=vocab, d=640, n_layer=6, n_head=5, multiple_of=256, eps=1e-5).cuda()
+    step_model = torch.compile(model) if args.compile else model
+    opt = torch.optim.AdamW(model.parameters(), lr=1.2e-3, fused=True)
+    idx = torch.randint(0, vocab, (batch, seq), device="cuda")
+    tgt = torch.randint(0, vocab, (batch, seq), device="cuda")
+
+    def step():
+        opt.zero_grad(set_to_none=True)
+        with torch.autocast("cuda", dtype=torch.bfloat16):
+            loss = step_model(idx, tgt)
+            loss.backward()
+        opt.step()
+        return loss
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    torch.cuda.synchronize()
+    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    s.record()
+    for _ in range(args.steps):
+        loss = step()
+    e.record()
+    torch.cuda.synchronize()
+    ms = s.elapsed_time(e) / args.steps
+    tokens = batch * seq
+    lin_flops = sum(6.0 * tokens * k * n for k, n in ((640, 1920), (640, 640), (640, 3584), (1792, 640))) * 6
+    print(json.dumps({
+        "metric": "llama30m_train_step_tokens_per_s", "value": round(tokens / (ms * 1e-3), 1), "unit": "tokens/s", "n_gpus": 1,
+        "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": round(ms, 3), "higher_is_better": True, "dtype": "mxfp4 linears, bf16 autocast",
+        "data": "synthetic", "compiled": bool(args.compile), "loss": round(loss.item(), 4),
+        "config": {"workload": "llama30m_step", "model": "6 blocks, width 640, 5 heads, SwiGLU 1792, vocabulary 32000 (71 M parameters)",
+                   "global_batch": batch, "seq_len": seq, "optimizer": "AdamW (fused)"},
+        "quantized_linear_tflops_at_this_step_time": round(lin_flops / (ms * 1e-3) / 1e12, 1),
+        "device_fault_word": ops.device_status(),
+    }), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default=WORKLOAD, choices=sorted(WORKLOADS))
+    ap.add_argument("--workload", default=WORKLOAD, choices=sorted(WORKLOADS) + ["llama30m_step"])
+    ap.add_argument("--compile", action="store_true", help="llama30m_step only: run the model under torch.compile")
     ap.add_argument("--exchange", default="auto", choices=["auto", "peer", "copy", "nccl"],
                     help="wgrad exchange for --gpus > 1 (auto = copy: DMA engines push each owner's rows)")
     args = ap.parse_args()
+    if args.workload == "llama30m_step":
+        if args.impl == "reference" or int(os.environ.get("WORLD_SIZE", "1")) > 1:
+            raise SystemExit("llama30m_step is a one-GPU workload of this library's arm")
+        return model_step_arm(args)
     if args.impl == "reference":
         if int(os.environ.get("RANK", "0")) != 0:
             return
