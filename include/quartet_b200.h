@@ -141,6 +141,30 @@ int quartet_gemm_mxfp4_tn(const uint8_t* a, const uint8_t* a_sf, const uint8_t* 
                           int d_dtype, quartet_stream_t stream);
 
 /*
+ * The whole layer in one host call per direction: exactly the kernel sequences the entry points above launch one
+ * by one, for callers whose per-call cost matters (a Python caller pays tens of microseconds per entry point).
+ *
+ * quartet_linear_fwd = QuantizedLinear.forward with the forward quantizer on both operands
+ * (src/models/quantization/__init__.py:36-42): (xc, xs, xm) = quant_fwd(x [M, K]), (wc, ws, wm) = quant_fwd(w [N, K]),
+ * y [M, N] = gemm(xc, wc).  The six packed outputs are what the backward needs.  M, N, K multiples of 128.
+ *
+ * quartet_linear_bwd = QEQWtt_QEtQXttFn.backward (backward.py:64-85) followed by the straight-through backward of both
+ * forward quantizers (mxfp4.py:142-146): dx [M, K] and dw [N, K] from e [M, N] and the packed outputs of the forward.
+ * dx or dw may be NULL (not computed).  seeds4 is a HOST array of four seeds, used in the reference's call order
+ * E, Wq^T, E^T, Xq^T; rounding 0, 1 or 3.  alpha = (4/3 * out_scale)^2.  workspace: device memory, 256-byte aligned, of
+ * quartet_linear_bwd_workspace_bytes(M, N, K) bytes (the packed operands of the two backward GEMMs).
+ */
+int quartet_linear_fwd(const void* x, int x_dtype, const void* w, int w_dtype, int64_t M, int64_t N, int64_t K,
+                       float had_scale_x, float had_scale_w, float gaussian_scale, uint8_t* xc, uint8_t* xs, uint8_t* xm,
+                       uint8_t* wc, uint8_t* ws, uint8_t* wm, void* y, int y_dtype, quartet_stream_t stream);
+int64_t quartet_linear_bwd_workspace_bytes(int64_t M, int64_t N, int64_t K);
+int quartet_linear_bwd(const void* e, int e_dtype, int64_t M, int64_t N, int64_t K, const uint8_t* xc, const uint8_t* xs,
+                       const uint8_t* xm, const uint8_t* wc, const uint8_t* ws, const uint8_t* wm, float had_scale_b,
+                       uint32_t signs, const uint32_t* signs_dev, int rounding, const uint64_t* seeds4, uint64_t offset,
+                       float alpha, float had_scale_x, float had_scale_w, uint8_t* workspace, void* dx, int dx_dtype, void* dw,
+                       int dw_dtype, quartet_stream_t stream);
+
+/*
  * Stand-alone straight-through backward of the forward quantizer:
  * out = ((g * mask).view(-1,32) @ H^T).view(rows, cols)  (mxfp4.py:142-146); mask NULL = all ones
  * (AlbertTsengQuantizerFn.backward, mxfp4.py:30-34).  cols % 32 == 0.

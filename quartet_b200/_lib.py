@@ -34,6 +34,10 @@ SIGNATURES = {
     "quartet_probe_copy_ingress_noalloc": (_i, [_p, _u64, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.POINTER(C.c_double), _p]),
     "quartet_fold_signs": (_i, [_p, _i, _p, _p]),
     "quartet_selftest_wait_timeout": (_i, [_p, _p]),
+    "quartet_linear_fwd": (_i, [_p, _i, _p, _i, _i64, _i64, _i64, _f, _f, _f, _p, _p, _p, _p, _p, _p, _p, _i, _p]),
+    "quartet_linear_bwd_workspace_bytes": (_i64, [_i64, _i64, _i64]),
+    "quartet_linear_bwd": (_i, [_p, _i, _i64, _i64, _i64, _p, _p, _p, _p, _p, _p, _f, _u32, _p, _i, C.POINTER(C.c_uint64), _u64, _f, _f, _f, _p,
+                                _p, _i, _p, _i, _p]),
     "quartet_unrotate_mask": (_i, [_p, _i, _p, _i64, _i64, _f, _p, _i, _p]),
     "quartet_dequant": (_i, [_p, _p, _i64, _i64, _f, _p, _i, _p]),
     "quartet_sf_offset": (_i64, [_i64, _i64, _i64]),

@@ -183,6 +183,50 @@ def gemm_mxfp4_tn(a, a_sf, b, b_sf, alpha=1.0, mask=None, had_scale=HAD_SCALE_BF
     return out
 
 
+# One host call per direction for the whole layer (quartet_linear_fwd / quartet_linear_bwd): the same kernels as the
+# single entry points.  FUSED_LAYER_CALLS = False makes the layer code call the entry points one by one instead
+# (what the benchmark's per-kernel timing pass does).
+FUSED_LAYER_CALLS = True
+
+
+def linear_fwd(x2, w, had_scale_x, had_scale_w, out_dtype, gaussian_scale=QUEST_GAUSSIAN_SCALE):
+    """x2 [M, K] (M a multiple of 128), w [N, K] -> (y [M, N], xc, xs, xm, wc, ws, wm)."""
+    _need_cuda(x2, w)
+    M, K = x2.shape
+    N = w.shape[0]
+    dev = x2.device
+    u8 = torch.uint8
+    xc, xs, xm = torch.empty(M, K // 2, dtype=u8, device=dev), torch.empty(sf_bytes(M, K), dtype=u8, device=dev), torch.empty(M, K // 8, dtype=u8, device=dev)
+    wc, ws, wm = torch.empty(N, K // 2, dtype=u8, device=dev), torch.empty(sf_bytes(N, K), dtype=u8, device=dev), torch.empty(N, K // 8, dtype=u8, device=dev)
+    y = torch.empty(M, N, dtype=out_dtype, device=dev)
+    with _on(dev):
+        rc = _lib.load().quartet_linear_fwd(_ptr(x2), _dt(x2), _ptr(w), _dt(w), M, N, K, had_scale_x, had_scale_w, gaussian_scale, _ptr(xc), _ptr(xs),
+                                            _ptr(xm), _ptr(wc), _ptr(ws), _ptr(wm), _ptr(y), _out_dt(out_dtype), _stream())
+    _lib.check(rc, "quartet_linear_fwd")
+    return y, xc, xs, xm, wc, ws, wm
+
+
+def linear_bwd(e2, xc, xs, xm, wc, ws, wm, had_scale_b, rounding, seeds, alpha, had_scale_x, had_scale_w, x_dtype, w_dtype, need_dx=True,
+               need_dw=True, signs=0, signs_dev=None, offset=0):
+    """e2 [M, N] (M a multiple of 128) and the packed outputs of linear_fwd -> (dx [M, K] | None, dw [N, K] | None)."""
+    _need_cuda(e2, xc, xs, xm, wc, ws, wm, signs_dev)
+    M, N = e2.shape
+    K = wc.shape[1] * 2
+    dev = e2.device
+    lib = _lib.load()
+    work = torch.empty(lib.quartet_linear_bwd_workspace_bytes(M, N, K), dtype=torch.uint8, device=dev)
+    dx = torch.empty(M, K, dtype=x_dtype, device=dev) if need_dx else None
+    dw = torch.empty(N, K, dtype=w_dtype, device=dev) if need_dw else None
+    m64 = 2**64 - 1
+    seeds4 = (C.c_uint64 * 4)(*[int(v) & m64 for v in seeds])
+    with _on(dev):
+        rc = lib.quartet_linear_bwd(_ptr(e2), _dt(e2), M, N, K, _ptr(xc), _ptr(xs), _ptr(xm), _ptr(wc), _ptr(ws), _ptr(wm), had_scale_b,
+                                    int(signs) & 0xFFFFFFFF, _ptr(signs_dev), rounding, seeds4, int(offset) & m64, alpha, had_scale_x, had_scale_w,
+                                    _ptr(work), _ptr(dx), _out_dt(x_dtype), _ptr(dw), _out_dt(w_dtype), _stream())
+    _lib.check(rc, "quartet_linear_bwd")
+    return dx, dw
+
+
 def gemm_mxfp4_tn_scatter(a, a_sf, b, b_sf, owner_ptrs, rows_per_owner, alpha=1.0, mask=None, had_scale=HAD_SCALE_BF16):
     """The fp32 product of `gemm_mxfp4_tn` with rows [o*rows_per_owner, (o+1)*rows_per_owner) stored to the
     device address owner_ptrs[o] (a dense [rows_per_owner, N] matrix, possibly in another GPU's memory)."""

@@ -38,9 +38,12 @@ class QuartetLinearFn(torch.autograd.Function):
         m_real = x2.shape[0]
         x2 = _pad_rows(x2.contiguous())
         wc_ = w.contiguous()
-        xc, xs, xm = ops.quant_fwd(x2, a_q.had_scale, ops.QUEST_GAUSSIAN_SCALE, return_mask=True)
-        wc, ws, wm = ops.quant_fwd(wc_, w_q.had_scale, ops.QUEST_GAUSSIAN_SCALE, return_mask=True)
-        y = ops.gemm_mxfp4_tn(xc, xs, wc, ws, 1.0, out_dtype=out_dtype)
+        if ops.FUSED_LAYER_CALLS:  # one host call for the three launches
+            y, xc, xs, xm, wc, ws, wm = ops.linear_fwd(x2, wc_, a_q.had_scale, w_q.had_scale, out_dtype)
+        else:
+            xc, xs, xm = ops.quant_fwd(x2, a_q.had_scale, ops.QUEST_GAUSSIAN_SCALE, return_mask=True)
+            wc, ws, wm = ops.quant_fwd(wc_, w_q.had_scale, ops.QUEST_GAUSSIAN_SCALE, return_mask=True)
+            y = ops.gemm_mxfp4_tn(xc, xs, wc, ws, 1.0, out_dtype=out_dtype)
         ctx.save_for_backward(xc, xs, xm, wc, ws, wm)
         ctx.a_q, ctx.w_q, ctx.g_q = a_q, w_q, g_q
         ctx.x_shape, ctx.m_real = x.shape, m_real
@@ -67,6 +70,12 @@ class QuartetLinearFn(torch.autograd.Function):
         sg = g_q.sign_args()
         hb = g_q.had_scale
         alpha = (ops.SR_OPERAND_SCALE * g_q.out_scale) ** 2
+        if ops.FUSED_LAYER_CALLS and ctx.wgrad_sink is None and rounding in (ops.ROUND_NEAREST, ops.ROUND_SR_PHILOX, ops.ROUND_SR_TLRAND):
+            dx, dw = ops.linear_bwd(e2, xc, xs, xm, wc, ws, wm, hb, rounding, seeds, alpha, ctx.a_q.had_scale, ctx.w_q.had_scale, ctx.x_dtype,
+                                    ctx.w_dtype, ctx.needs_input_grad[0], ctx.needs_input_grad[1], **sg)
+            if dx is not None:
+                dx = dx[:ctx.m_real].reshape(ctx.x_shape)
+            return dx, dw, None, None, None, None, None
         dx = dw = None
         dual = None
         if ctx.needs_input_grad[0] and ctx.needs_input_grad[1] and rounding in (ops.ROUND_NEAREST, ops.ROUND_SR_PHILOX):

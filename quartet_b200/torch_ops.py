@@ -181,9 +181,12 @@ def linear_fwd(x: Tensor, w: Tensor, handle: int, out_dtype: torch.dtype) -> Tup
     wq._see(w)
     K = w.shape[1]
     x2 = _pad_rows(x.reshape(-1, K).contiguous())
-    xc, xs, xm = ops.quant_fwd(x2, aq.had_scale, ops.QUEST_GAUSSIAN_SCALE, return_mask=True)
-    wc, ws, wm = ops.quant_fwd(w.contiguous(), wq.had_scale, ops.QUEST_GAUSSIAN_SCALE, return_mask=True)
-    y = ops.gemm_mxfp4_tn(xc, xs, wc, ws, 1.0, out_dtype=out_dtype)
+    if ops.FUSED_LAYER_CALLS:
+        y, xc, xs, xm, wc, ws, wm = ops.linear_fwd(x2, w.contiguous(), aq.had_scale, wq.had_scale, out_dtype)
+    else:
+        xc, xs, xm = ops.quant_fwd(x2, aq.had_scale, ops.QUEST_GAUSSIAN_SCALE, return_mask=True)
+        wc, ws, wm = ops.quant_fwd(w.contiguous(), wq.had_scale, ops.QUEST_GAUSSIAN_SCALE, return_mask=True)
+        y = ops.gemm_mxfp4_tn(xc, xs, wc, ws, 1.0, out_dtype=out_dtype)
     m_real = x.numel() // K
     y = y[:m_real].reshape(*x.shape[:-1], w.shape[0])
     if m_real != y.shape[0] or not y.is_contiguous():
@@ -224,6 +227,17 @@ def linear_bwd(e: Tensor, xc: Tensor, xs: Tensor, xm: Tensor, wc: Tensor, ws: Te
     sg = g_q.sign_args()
     hb = g_q.had_scale
     alpha = (ops.SR_OPERAND_SCALE * g_q.out_scale) ** 2
+    if ops.FUSED_LAYER_CALLS and rounding in (ops.ROUND_NEAREST, ops.ROUND_SR_PHILOX, ops.ROUND_SR_TLRAND):
+        dx, dw = ops.linear_bwd(e2, xc, xs, xm, wc, ws, wm, hb, rounding, seeds, alpha, aq.had_scale, wq.had_scale, x_dtype, w_dtype, need_dx,
+                                need_dw, **sg)
+        if dx is not None and m_real != dx.shape[0]:
+            dx = dx[:m_real].contiguous()
+        if dx is None:
+            dx = e.new_empty((0,), dtype=x_dtype)
+        if dw is None:
+            dw = e.new_empty((0,), dtype=w_dtype)
+        ops.raise_on_fault("QuantizedLinear backward")  # only with QUARTET_CHECK_FAULTS=1
+        return dx, dw
     dual = None
     if need_dx and need_dw and rounding in (ops.ROUND_NEAREST, ops.ROUND_SR_PHILOX):
         dual = ops.quant_bwd_dual(e2, hb, rounding=rounding, seed_rows=seeds[0], seed_t=seeds[2], **sg)
