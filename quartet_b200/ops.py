@@ -230,8 +230,6 @@ def linear_bwd(e2, xc, xs, xm, wc, ws, wm, had_scale_b, rounding, seeds, alpha, 
 def gemm_mxfp4_tn_scatter(a, a_sf, b, b_sf, owner_ptrs, rows_per_owner, alpha=1.0, mask=None, had_scale=HAD_SCALE_BF16):
     """The fp32 product of `gemm_mxfp4_tn` with rows [o*rows_per_owner, (o+1)*rows_per_owner) stored to the
     device address owner_ptrs[o] (a dense [rows_per_owner, N] matrix, possibly in another GPU's memory)."""
-    import ctypes as C
-
     _need_cuda(a, a_sf, b, b_sf, mask)
     M, K = a.shape[0], a.shape[1] * 2
     N = b.shape[0]
@@ -257,8 +255,6 @@ def shard_reduce(slots_ptr, n_slots, slot_elems, scale, out):
 
 def peer_alloc(nbytes, device):
     """(device address, 64-byte handle) of a buffer other processes of the node can map."""
-    import ctypes as C
-
     ptr, handle = C.c_void_p(), C.create_string_buffer(64)
     with torch.cuda.device(device):
         rc = _lib.load().quartet_peer_alloc(nbytes, C.byref(ptr), C.cast(handle, C.c_void_p))
@@ -267,8 +263,6 @@ def peer_alloc(nbytes, device):
 
 
 def peer_open(handle, device):
-    import ctypes as C
-
     ptr, buf = C.c_void_p(), C.create_string_buffer(bytes(handle), 64)
     with torch.cuda.device(device):
         rc = _lib.load().quartet_peer_open(C.cast(buf, C.c_void_p), C.byref(ptr))
@@ -294,8 +288,6 @@ def peer_free(ptr, device):
 
 def probe_copy_ingress(region_mb=48, iters=4000, stages=6, chunk=16384, producers=2, device="cuda"):
     """Bytes per clock one SM takes in through bulk asynchronous copies (see csrc/probe_ingress.cu)."""
-    import ctypes as C
-
     src = torch.ones(region_mb << 20, dtype=torch.uint8, device=device)
     cycles = torch.zeros(1024, dtype=torch.int64, device=device)
     out = C.c_double(0.0)
@@ -307,8 +299,6 @@ def probe_copy_ingress(region_mb=48, iters=4000, stages=6, chunk=16384, producer
 
 def probe_copy_ingress_noalloc(src, iters=4000, stages=6, chunk=16384, producers=2):
     """`probe_copy_ingress` on a caller-provided uint8 device tensor; neither this wrapper nor the library allocates."""
-    import ctypes as C
-
     _need_cuda(src)
     out = C.c_double(0.0)
     with torch.cuda.device(src.device):
