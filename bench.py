@@ -18,7 +18,8 @@ layer, X [8192, 640], W [2560, 640]), "llama30m_linears_32768tok" (the 24 block 
 block linears of a Llama-3-8B layer at 8 x 4096 tokens), and "llama30m_step": a whole training step
 (forward, backward under bf16 autocast, AdamW) of a 30M Llama-style model whose block linears are
 QuantizedLinear (6 blocks, width 640, 5 heads, SwiGLU 1792, vocabulary 32000, 64 x 512 uniform-random
-token ids; the model is the test harness tests/llama_harness.py; add --compile for torch.compile).
+token ids; the model is the test harness tests/llama_harness.py; add --compile for torch.compile and
+--fuse-producers for the norms and the SwiGLU product computed inside the forward quantizers).
 
 What the line reports:
   value      K steps with inputs resident in HBM, CUDA events, max over ranks
@@ -574,7 +575,7 @@ def model_step_arm(args):
     torch.cuda.set_device(0)
     torch.manual_seed(0)
     batch, seq, vocab = 64, 512, 32000
-    model = TinyLlama(Q, vocab=vocab, d=640, n_layer=6, n_head=5, multiple_of=256, eps=1e-5).cuda()
+    model = TinyLlama(Q, vocab=vocab, d=640, n_layer=6, n_head=5, multiple_of=256, eps=1e-5, fuse_producers=args.fuse_producers).cuda()
     step_model = torch.compile(model) if args.compile else model
     opt = torch.optim.AdamW(model.parameters(), lr=1.2e-3, fused=True)
     idx = torch.randint(0, vocab, (batch, seq), device="cuda")
@@ -603,7 +604,7 @@ def model_step_arm(args):
     print(json.dumps({
         "metric": "llama30m_train_step_tokens_per_s", "value": round(tokens / (ms * 1e-3), 1), "unit": "tokens/s", "n_gpus": 1,
         "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": round(ms, 3), "higher_is_better": True, "dtype": "mxfp4 linears, bf16 autocast",
-        "data": "synthetic", "compiled": bool(args.compile), "loss": round(loss.item(), 4),
+        "data": "synthetic", "compiled": bool(args.compile), "fuse_producers": bool(args.fuse_producers), "loss": round(loss.item(), 4),
         "config": {"workload": "llama30m_step", "model": "6 blocks, width 640, 5 heads, SwiGLU 1792, vocabulary 32000 (71 M parameters)",
                    "global_batch": batch, "seq_len": seq, "optimizer": "AdamW (fused)"},
         "quantized_linear_tflops_at_this_step_time": round(lin_flops / (ms * 1e-3) / 1e12, 1),
@@ -619,6 +620,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default=WORKLOAD, choices=sorted(WORKLOADS) + ["llama30m_step"])
     ap.add_argument("--compile", action="store_true", help="llama30m_step only: run the model under torch.compile")
+    ap.add_argument("--fuse-producers", action="store_true",
+                    help="llama30m_step only: RMSNorm and SwiGLU computed inside the forward quantizer of the layer they feed")
     ap.add_argument("--exchange", default="auto", choices=["auto", "peer", "copy", "nccl"],
                     help="wgrad exchange for --gpus > 1 (auto = copy: DMA engines push each owner's rows)")
     args = ap.parse_args()

@@ -66,6 +66,35 @@ int quartet_quant_fwd(const void* x, int x_dtype, int64_t rows, int64_t cols, fl
                       uint8_t* codes, uint8_t* sf, uint8_t* mask, quartet_stream_t stream);
 
 /*
+ * Forward quantizer fused into the elementwise step that produces its input: the activation of a
+ * quantized linear layer is quantized straight from the tensor the step reads, and is never
+ * written in bf16 / fp32.  Same outputs and output contract as quartet_quant_fwd.
+ *
+ * quartet_quant_fwd_rmsnorm: the input is RMSNorm(x) as src/models/llama.py:64-75 computes it,
+ *   (x * rsqrt(mean(x^2) + eps)).type_as(x) * weight      (weight: fp32 [cols]; result fp32),
+ * feeding c_attn (llama.py:124) and mlp.w12 (llama.py:113).  x: [rows, cols] bf16 / fp32,
+ * cols % 128 == 0.  rstd ([rows] fp32, required) receives rsqrt(mean(x^2) + eps) per row: the
+ * norm's backward needs it.  Two launches per chunk of rows (statistics, then quantization; the
+ * chunk is sized for the second read to come from L2).
+ * quartet_rms_stats: the statistics alone (cols % 8 == 0).
+ *
+ * quartet_quant_fwd_swiglu: the input is silu(h[:, :hidden]) * h[:, hidden:] (llama.py:112-114,
+ * feeding mlp.c_proj); h: [rows, 2 * hidden] bf16 / fp32 row-major, hidden % 128 == 0.  For bf16
+ * the value of silu and the product are each rounded to bf16, as the two torch kernels round them;
+ * silu is x / (1 + exp(-x)) in fp32.
+ */
+int quartet_rms_stats(const void* x, int x_dtype, int64_t rows, int64_t cols, float eps, float* rstd, quartet_stream_t stream);
+int quartet_quant_fwd_rmsnorm(const void* x, int x_dtype, int64_t rows, int64_t cols, const float* weight, float eps, float* rstd,
+                              float had_scale, float gaussian_scale, uint8_t* codes, uint8_t* sf, uint8_t* mask,
+                              quartet_stream_t stream);
+int quartet_quant_fwd_swiglu(const void* h, int h_dtype, int64_t rows, int64_t hidden, float had_scale, float gaussian_scale,
+                             uint8_t* codes, uint8_t* sf, uint8_t* mask, quartet_stream_t stream);
+/* The same product written out as [rows, hidden] in h's dtype (hidden % 8 == 0): the values the fused quantizer
+ * quantizes, for callers that need the activation itself, and the handle by which the tests pin its arithmetic to
+ * torch's (all 65536 bf16 inputs of silu). */
+int quartet_swiglu(const void* h, int h_dtype, int64_t rows, int64_t hidden, void* out, quartet_stream_t stream);
+
+/*
  * Backward quantizer, row-wise: rotation (H @ diag(signs)), absmax scale
  * E8M0 = floor(log2 amax) - 2, rounding per `rounding`.  The 4/3 of the reference's
  * shared exponent (2^e / 0.75) is NOT in the scale bytes; fold it into the GEMM alpha.

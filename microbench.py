@@ -1,6 +1,8 @@
 """Kernel-level micro-benchmark of the path, one kernel per run:
 
     python microbench.py --kernel quant_fwd  --rows 16384 --cols 4096 [--dtype bf16|f32]
+    python microbench.py --kernel quant_fwd_rmsnorm --rows 16384 --cols 4096 --dtype f32   (rmsnorm_then_quant: the unfused sequence)
+    python microbench.py --kernel quant_fwd_swiglu  --rows 16384 --cols 11008              (swiglu_then_quant: the unfused sequence)
     python microbench.py --kernel quant_bwd  --rows 16384 --cols 12288 [--rounding 1]
     python microbench.py --kernel quant_bwd_t --rows 16384 --cols 12288
     python microbench.py --kernel requant_t  --rows 16384 --cols 4096
@@ -26,7 +28,7 @@ sys.path.insert(0, ROOT)
 
 from quartet_b200 import ops  # noqa: E402
 
-BYTES_PER_ELEM = {"quant_fwd": 0.5 + 1 / 32 + 1 / 8, "quant_bwd": 0.5 + 1 / 32, "quant_bwd_t": 0.5 + 1 / 32,
+BYTES_PER_ELEM = {"quant_fwd": 0.5 + 1 / 32 + 1 / 8, "quant_fwd_rmsnorm": 0.5 + 1 / 32 + 1 / 8, "quant_fwd_swiglu": 0.5 + 1 / 32 + 1 / 8, "quant_bwd": 0.5 + 1 / 32, "quant_bwd_t": 0.5 + 1 / 32,
                   "quant_bwd_dual": 2 * (0.5 + 1 / 32)}
 
 
@@ -112,17 +114,35 @@ def run_quant(kernel, rows, cols, dtype, rounding, iters, warmup, gauss, flush=T
         x = make_input(rows, cols, dtype, gauss)
         if kernel == "quant_fwd":
             fn = lambda: ops.quant_fwd(x, ops.HAD_SCALE_BF16 if esz == 2 else ops.HAD_SCALE_F32)  # noqa: E731
+        elif kernel in ("quant_fwd_rmsnorm", "rmsnorm_then_quant"):
+            # cols = width of the normalised rows; bytes: the rows once (their second read is meant to come from L2)
+            w = torch.ones(cols, device="cuda")
+            if kernel == "quant_fwd_rmsnorm":
+                fn = lambda: ops.quant_fwd_rmsnorm(x, w, 1e-5, ops.HAD_SCALE_F32)  # noqa: E731
+            else:  # the unfused sequence, for comparison: torch's RMSNorm (llama.py:64-75 of the reference), then the plain quantizer
+                fn = lambda: ops.quant_fwd((x.float() * torch.rsqrt(x.float().pow(2).mean(-1, keepdim=True) + 1e-5)).type_as(x) * w, ops.HAD_SCALE_F32)  # noqa: E731
+            kernel_bytes = "quant_fwd_rmsnorm"
+        elif kernel in ("quant_fwd_swiglu", "swiglu_then_quant"):
+            # cols = hidden width; the input holds up and gate side by side
+            del x
+            x = make_input(rows, 2 * cols, dtype, True)
+            if kernel == "quant_fwd_swiglu":
+                fn = lambda: ops.quant_fwd_swiglu(x, ops.HAD_SCALE_BF16 if esz == 2 else ops.HAD_SCALE_F32)  # noqa: E731
+            else:
+                fn = lambda: ops.quant_fwd(torch.nn.functional.silu(x[:, :cols]) * x[:, cols:], ops.HAD_SCALE_BF16 if esz == 2 else ops.HAD_SCALE_F32)  # noqa: E731
+            kernel_bytes = "quant_fwd_swiglu"
+            esz *= 2
         elif kernel == "quant_bwd":
             fn = lambda: ops.quant_bwd(x, rounding=rounding, seed=1)  # noqa: E731
         elif kernel == "quant_bwd_dual":
             fn = lambda: ops.quant_bwd_dual(x, rounding=rounding, seed_rows=1, seed_t=2)  # noqa: E731
         else:
             fn = lambda: ops.quant_bwd_t(x, rounding=rounding, seed=1)  # noqa: E731
-        bytes_ = rows * cols * (esz + BYTES_PER_ELEM[kernel])
+        bytes_ = rows * cols * (esz + BYTES_PER_ELEM[kernel_bytes if kernel not in BYTES_PER_ELEM else kernel])
     avg, best = time_kernel(fn, iters, warmup, flush)
     hbm = _peaks().get("hbm_gbs", 6650.0)
     gbs = bytes_ / (avg * 1e-3) / 1e9
-    return {"kernel": kernel, "rows": rows, "cols": cols, "dtype": "bf16" if esz == 2 else "f32", "rounding": rounding, "l2_flushed_between_launches": bool(flush),
+    return {"kernel": kernel, "rows": rows, "cols": cols, "dtype": "bf16" if dtype == torch.bfloat16 else "f32", "rounding": rounding, "l2_flushed_between_launches": bool(flush),
             "avg_ms": round(avg, 4), "best_ms": round(best, 4), "GB/s": round(gbs, 1), "frac_of_hbm_peak": round(gbs / hbm, 4),
             "algorithmic_bytes": int(bytes_)}
 
@@ -147,7 +167,7 @@ def run_gemm(m, n, k, iters, warmup, fused, out_f32, flush=True):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--kernel", default="quant_fwd", choices=["quant_fwd", "quant_bwd", "quant_bwd_t", "quant_bwd_dual", "requant_t", "gemm", "copy_ingress"])
+    ap.add_argument("--kernel", default="quant_fwd", choices=["quant_fwd", "quant_fwd_rmsnorm", "rmsnorm_then_quant", "quant_fwd_swiglu", "swiglu_then_quant", "quant_bwd", "quant_bwd_t", "quant_bwd_dual", "requant_t", "gemm", "copy_ingress"])
     ap.add_argument("--rows", type=int, default=16384)
     ap.add_argument("--cols", type=int, default=4096)
     ap.add_argument("--m", type=int, default=16384)

@@ -357,6 +357,21 @@ def unrotate_mask(g: torch.Tensor, mask: torch.Tensor, h: torch.Tensor) -> torch
     return ((g.to(torch.float32) * mask.to(torch.float32)).reshape(-1, GROUP) @ h.T).reshape(shape)
 
 
+def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, rstd: torch.Tensor | None = None) -> torch.Tensor:
+    """RMSNorm as src/models/llama.py:64-75 of the reference states it: `_norm(x.float()).type_as(x) * weight`.
+    With `rstd` given (one fp32 value per row) it replaces `rsqrt(mean(x^2) + eps)`: the remaining steps are
+    elementwise and identical on every device, which is what lets a test pin the fused kernel bit for bit."""
+    xf = x.float()
+    r = torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps) if rstd is None else rstd.reshape(-1, 1).float()
+    return (xf * r).type_as(x) * weight
+
+
+def swiglu(h: torch.Tensor) -> torch.Tensor:
+    """`silu(up) * gate` with up, gate the two halves of the last axis (src/models/llama.py:112-114)."""
+    up, gate = h.split(h.shape[-1] // 2, dim=-1)
+    return torch.nn.functional.silu(up) * gate
+
+
 def linear_forward(x, w, h_f):
     """QuantizedLinear.forward (quantization/__init__.py:36-42) with the Quest quantizer on both operands."""
     xq = quant_fwd(x, h_f)

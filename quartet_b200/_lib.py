@@ -17,6 +17,10 @@ _p, _i, _i64, _u32, _u64, _f = C.c_void_p, C.c_int, C.c_int64, C.c_uint32, C.c_u
 # name -> (restype, argtypes); mirrors include/quartet_b200.h one to one
 SIGNATURES = {
     "quartet_quant_fwd": (_i, [_p, _i, _i64, _i64, _f, _f, _p, _p, _p, _p]),
+    "quartet_rms_stats": (_i, [_p, _i, _i64, _i64, _f, _p, _p]),
+    "quartet_quant_fwd_rmsnorm": (_i, [_p, _i, _i64, _i64, _p, _f, _p, _f, _f, _p, _p, _p, _p]),
+    "quartet_quant_fwd_swiglu": (_i, [_p, _i, _i64, _i64, _f, _f, _p, _p, _p, _p]),
+    "quartet_swiglu": (_i, [_p, _i, _i64, _i64, _p, _p]),
     "quartet_quant_bwd": (_i, [_p, _i, _i64, _i64, _f, _u32, _p, _i, _u64, _u64, _p, _p, _p, _p]),
     "quartet_quant_group32": (_i, [_p, _i, _i64, _i64, _i, _f, _i, _u64, _u64, _p, _p, _p, _p, _p]),
     "quartet_quant_bwd_t": (_i, [_p, _i, _i64, _i64, _f, _u32, _p, _i, _u64, _u64, _p, _p, _p, _p]),

@@ -18,7 +18,7 @@ PKG = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(PKG, "csrc")
 OUT_DIR = os.path.join(PKG, "lib")
 LIB = os.path.join(OUT_DIR, "libquartet_b200.so")
-SOURCES = ["capi.cu", "quant_rows.cu", "quant_tile_t.cu", "aux_kernels.cu", "gemm_mxfp4.cu", "peer.cu", "probe_ingress.cu", "layer.cu"]
+SOURCES = ["capi.cu", "quant_rows.cu", "quant_producer.cu", "quant_tile_t.cu", "aux_kernels.cu", "gemm_mxfp4.cu", "peer.cu", "probe_ingress.cu", "layer.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden",

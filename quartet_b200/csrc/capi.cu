@@ -143,6 +143,7 @@ extern "C" __attribute__((visibility("default"))) int quartet_device_status(int3
     if ((rc = status_gemm(status))) return rc;
     if ((rc = status_aux(status))) return rc;
     if ((rc = status_probe(status))) return rc;
+    if ((rc = status_producer(status))) return rc;
     return QUARTET_OK;
 }
 

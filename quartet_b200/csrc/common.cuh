@@ -32,6 +32,7 @@ int status_tile_t(int32_t* out);
 int status_gemm(int32_t* out);
 int status_aux(int32_t* out);
 int status_probe(int32_t* out);
+int status_producer(int32_t* out);
 
 // cudaFuncSetAttribute(MaxDynamicSharedMemorySize) once per kernel instantiation, thread and device instead of
 // before every launch.  `state` is a thread_local int of the calling (template) function, initialised to -1.

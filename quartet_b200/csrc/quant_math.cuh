@@ -228,6 +228,63 @@ __device__ __forceinline__ uint32_t spread_sign_bits(uint32_t s8) {
 }
 
 // ---------------------------------------------------------------------------
+// Forward ("Quest") quantization of one group of 32 (mxfp4_triton.py:33-57,130-174 of the reference): rotate,
+// scale by the power of two at or below gaussian_scale * std + 1e-8, round to nearest with ties toward zero, and
+// report which values lie strictly inside the grid (|v| < 6) as 32 mask bits.  w holds the group on entry and
+// the rotated values on return.  ROT = false skips the rotation (h must then be 1).
+// ---------------------------------------------------------------------------
+template <bool ROT>
+__device__ __forceinline__ void quest_quantize_group(float (&w)[32], float h, float gaussian_scale, uint32_t (&words)[4],
+                                                     uint32_t& mbits, int& e8m0) {
+    // statistics that do not need the rotated values: sum_j xh_j = 32 h x_0 (only row 0 of the
+    // Sylvester matrix has a non-zero column sum) and sum_j xh_j^2 = 32 h^2 sum_i x_i^2 (Parseval).
+    float x0 = w[0];
+    if (!ROT) {
+        // no rotation: the group's own sum takes the place of 32 h x_0 (h = 1 here, see below)
+        float s = 0.f;
+#pragma unroll
+        for (int i = 0; i < 32; ++i) s += w[i];
+        x0 = s * (1.0f / 32.0f);
+    }
+    // two interleaved partial sums (even / odd elements) in one packed accumulator
+    f32x2_t acc = pack2(0.f, 0.f);
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+        const f32x2_t pr = pack2(w[2 * i], w[2 * i + 1]);
+        acc = fma2(pr, pr, acc);
+    }
+    float s_even, s_odd;
+    unpack2(acc, s_even, s_odd);
+    const float sumsq = s_even + s_odd;
+    if (ROT) wht32(w);
+
+    // rotated: sum_j xh_j = 32 h x_0 and sum_j xh_j^2 = 32 h^2 sum_i x_i^2; un-rotated (h = 1): the plain moments
+    const float mean = ROT ? h * x0 : x0;
+    const float mean_sq = ROT ? (h * h) * sumsq : sumsq * (1.0f / 32.0f);
+    const float var = fmaxf(mean_sq - mean * mean, 0.f);
+    const float scales = gaussian_scale * sqrtf(var) + 1e-8f;
+    e8m0 = exp_field(scales);
+    const float c = h * pow2_biased(254 - e8m0);  // h * 2^-e
+    float v[32];
+    const f32x2_t c2 = pack2(c, c), m36 = pack2(-36.f, -36.f);
+    // mask bit = |v| < 6  <=>  v * v - 36 < 0; the fused multiply-add rounds the exact difference, so its
+    // sign is exact (and |v| == 6 gives +0: clipped, as in the reference's strict `<`)
+    mbits = 0;
+#pragma unroll
+    for (int i = 15; i >= 0; --i) {
+        const f32x2_t vp = mul2(pack2(w[2 * i], w[2 * i + 1]), c2);
+        unpack2(vp, v[2 * i], v[2 * i + 1]);
+        float t0, t1;
+        unpack2(fma2(vp, vp, m36), t0, t1);
+        mbits = __funnelshift_l(__float_as_uint(t1), mbits, 1);
+        mbits = __funnelshift_l(__float_as_uint(t0), mbits, 1);
+    }
+#pragma unroll
+    for (int q = 0; q < 4; ++q) words[q] = cvt_e2m1x8_ties_down(&v[8 * q]);
+    // (the reference gives exact zeros a minus sign, `v > 0 ? + : -`; here +0 stays +0)
+}
+
+// ---------------------------------------------------------------------------
 // Backward (absmax-scaled) quantization of one rotated group.
 //   w      unnormalised WHT output; the rotated values are h * w
 //   g      index of the group in the OUTPUT tensor (row-major over [out_rows, out_cols/32]);

@@ -90,59 +90,13 @@ __global__ void __launch_bounds__(ROWS_THREADS, F32 ? 3 : 4) quant_rows_kernel(c
         const int gk = (warp >> 2) * 2 + it;  // group within the tile row, 0..3
         float w[32];
         load_row_group<F32>(s_in, row, gk, w);
-        // statistics that do not need the rotated values: sum_j xh_j = 32 h x_0 (only row 0 of the
-        // Sylvester matrix has a non-zero column sum) and sum_j xh_j^2 = 32 h^2 sum_i x_i^2 (Parseval).
-        float x0 = w[0];
-        float sumsq = 0.f;
-        if (KIND == KIND_QUEST && !ROT) {
-            // no rotation: the group's own sum takes the place of 32 h x_0 (h = 1 here, see below)
-            float s = 0.f;
-#pragma unroll
-            for (int i = 0; i < 32; ++i) s += w[i];
-            x0 = s * (1.0f / 32.0f);
-        }
-        if (KIND == KIND_QUEST) {
-            // two interleaved partial sums (even / odd elements) in one packed accumulator
-            f32x2_t acc = pack2(0.f, 0.f);
-#pragma unroll
-            for (int i = 0; i < 16; ++i) {
-                const f32x2_t pr = pack2(w[2 * i], w[2 * i + 1]);
-                acc = fma2(pr, pr, acc);
-            }
-            float s_even, s_odd;
-            unpack2(acc, s_even, s_odd);
-            sumsq = s_even + s_odd;
-        }
-        if (ROT) wht32(w);
-
         uint32_t words[4];
         uint32_t mbits = 0;
         int e8m0;
         if (KIND == KIND_QUEST) {
-            // rotated: sum_j xh_j = 32 h x_0 and sum_j xh_j^2 = 32 h^2 sum_i x_i^2; un-rotated (h = 1): the plain moments
-            const float mean = ROT ? h * x0 : x0;
-            const float mean_sq = ROT ? (h * h) * sumsq : sumsq * (1.0f / 32.0f);
-            const float var = fmaxf(mean_sq - mean * mean, 0.f);
-            const float scales = p.gaussian_scale * sqrtf(var) + 1e-8f;
-            e8m0 = exp_field(scales);
-            const float c = h * pow2_biased(254 - e8m0);  // h * 2^-e
-            float v[32];
-            const f32x2_t c2 = pack2(c, c), m36 = pack2(-36.f, -36.f);
-            // mask bit = |v| < 6  <=>  v * v - 36 < 0; the fused multiply-add rounds the exact difference, so its
-            // sign is exact (and |v| == 6 gives +0: clipped, as in the reference's strict `<`)
-#pragma unroll
-            for (int i = 15; i >= 0; --i) {
-                const f32x2_t vp = mul2(pack2(w[2 * i], w[2 * i + 1]), c2);
-                unpack2(vp, v[2 * i], v[2 * i + 1]);
-                float t0, t1;
-                unpack2(fma2(vp, vp, m36), t0, t1);
-                mbits = __funnelshift_l(__float_as_uint(t1), mbits, 1);
-                mbits = __funnelshift_l(__float_as_uint(t0), mbits, 1);
-            }
-#pragma unroll
-            for (int q = 0; q < 4; ++q) words[q] = cvt_e2m1x8_ties_down(&v[8 * q]);
-            // (the reference gives exact zeros a minus sign, `v > 0 ? + : -`; here +0 stays +0)
+            quest_quantize_group<ROT>(w, h, p.gaussian_scale, words, mbits, e8m0);
         } else {
+            if (ROT) wht32(w);
             const uint64_t g = (uint64_t)grow * (uint64_t)(p.cols >> 5) + (uint64_t)((col0 >> 5) + gk);
             const int64_t flat = grow * p.cols + col0 + gk * 32;
             absmax_quantize_group<ROUND>(w, h, g, flat, grow < p.rows, p.seed, p.offset, p.noise, flip, words, e8m0);

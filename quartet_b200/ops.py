@@ -86,6 +86,65 @@ def quant_fwd(x, had_scale=HAD_SCALE_BF16, gaussian_scale=QUEST_GAUSSIAN_SCALE, 
     return codes, sf, mask
 
 
+def rms_stats(x, eps):
+    """rsqrt(mean(x^2, -1) + eps) per row of [rows, cols] (bf16 / fp32) -> fp32 [rows]."""
+    _need_cuda(x)
+    rows, cols = x.shape
+    rstd = torch.empty(rows, dtype=torch.float32, device=x.device)
+    with _on(x.device):
+        rc = _lib.load().quartet_rms_stats(_ptr(x), _dt(x), rows, cols, float(eps), _ptr(rstd), _stream())
+    _lib.check(rc, "quartet_rms_stats")
+    return rstd
+
+
+def quant_fwd_rmsnorm(x, weight, eps, had_scale=HAD_SCALE_BF16, gaussian_scale=QUEST_GAUSSIAN_SCALE, return_mask=True):
+    """Forward quantizer of RMSNorm(x) = (x * rstd).type_as(x) * weight without materialising it:
+    [rows, cols], fp32 weight [cols] -> (codes, sf blocked, mask | None, rstd fp32 [rows])."""
+    _need_cuda(x, weight)
+    rows, cols = x.shape
+    if weight.dtype != torch.float32 or weight.shape != (cols,) or not weight.is_contiguous():
+        raise ValueError("weight must be a contiguous fp32 vector with one entry per column")
+    codes = torch.empty(rows, cols // 2, dtype=torch.uint8, device=x.device)
+    sf = torch.empty(sf_bytes(rows, cols), dtype=torch.uint8, device=x.device)
+    mask = torch.empty(rows, cols // 8, dtype=torch.uint8, device=x.device) if return_mask else None
+    rstd = torch.empty(rows, dtype=torch.float32, device=x.device)
+    with _on(x.device):
+        rc = _lib.load().quartet_quant_fwd_rmsnorm(_ptr(x), _dt(x), rows, cols, _ptr(weight), float(eps), _ptr(rstd), had_scale, gaussian_scale,
+                                                   _ptr(codes), _ptr(sf), _ptr(mask), _stream())
+    _lib.check(rc, "quartet_quant_fwd_rmsnorm")
+    return codes, sf, mask, rstd
+
+
+def quant_fwd_swiglu(h, had_scale=HAD_SCALE_BF16, gaussian_scale=QUEST_GAUSSIAN_SCALE, return_mask=True):
+    """Forward quantizer of silu(h[:, :H]) * h[:, H:] without materialising it: [rows, 2H] -> (codes [rows, H/2], sf, mask | None)."""
+    _need_cuda(h)
+    rows, two_h = h.shape
+    if two_h % 2:
+        raise ValueError("h must hold the up and gate halves side by side")
+    hidden = two_h // 2
+    codes = torch.empty(rows, hidden // 2, dtype=torch.uint8, device=h.device)
+    sf = torch.empty(sf_bytes(rows, hidden), dtype=torch.uint8, device=h.device)
+    mask = torch.empty(rows, hidden // 8, dtype=torch.uint8, device=h.device) if return_mask else None
+    with _on(h.device):
+        rc = _lib.load().quartet_quant_fwd_swiglu(_ptr(h), _dt(h), rows, hidden, had_scale, gaussian_scale, _ptr(codes), _ptr(sf), _ptr(mask),
+                                                  _stream())
+    _lib.check(rc, "quartet_quant_fwd_swiglu")
+    return codes, sf, mask
+
+
+def swiglu(h):
+    """silu(h[:, :H]) * h[:, H:] written out, [rows, 2H] -> [rows, H] in h's dtype: the values quant_fwd_swiglu quantizes."""
+    _need_cuda(h)
+    rows, two_h = h.shape
+    if two_h % 2:
+        raise ValueError("h must hold the up and gate halves side by side")
+    out = torch.empty(rows, two_h // 2, dtype=h.dtype, device=h.device)
+    with _on(h.device):
+        rc = _lib.load().quartet_swiglu(_ptr(h), _dt(h), rows, two_h // 2, _ptr(out), _stream())
+    _lib.check(rc, "quartet_swiglu")
+    return out
+
+
 def _sr_args(signs, signs_dev, seed, offset, noise):
     return (int(signs) & 0xFFFFFFFF, _ptr(signs_dev)), (int(seed) & (2**64 - 1), int(offset) & (2**64 - 1), _ptr(noise))
 

@@ -17,6 +17,7 @@ import torch.nn as nn
 from .. import ops, torch_ops
 from .backward import BACKWARD_SCHEMES, EW_EtX_Scheme, QEQWtt_QEtQXtt_Scheme
 from .fused import QuartetLinearFn
+from .producers import rmsnorm_linear, swiglu_linear  # noqa: F401
 from .quantizers import (AbsmaxRotation32, AlbertTsengQuantizer, AlignedAlbertTsengQuantizer, BaseQuantizer, NoQuantizer,
                          QuestMXFP4Quantizer, mxfp4_forward_kernel_wrapper)
 

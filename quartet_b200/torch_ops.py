@@ -292,3 +292,130 @@ torch.library.register_autograd("quartet_b200::linear_fwd", _linear_backward, se
 def quantized_linear(x: Tensor, w: Tensor, handle: int, out_dtype: torch.dtype) -> Tensor:
     """y = QuantizedLinear(x) through the pair of operators above (differentiable, traceable)."""
     return torch.ops.quartet_b200.linear_fwd(x, w, handle, out_dtype)[0]
+
+
+# ------------------------------------------------------------------------------------------------
+# the layer with the forward quantizer fused into the elementwise step that produces its input
+# ------------------------------------------------------------------------------------------------
+def _weight_and_gemm(xc, xs, w, wq, out_dtype):
+    wc, ws, wm = ops.quant_fwd(w.contiguous(), wq.had_scale, ops.QUEST_GAUSSIAN_SCALE, return_mask=True)
+    return ops.gemm_mxfp4_tn(xc, xs, wc, ws, 1.0, out_dtype=out_dtype), wc, ws, wm
+
+
+def _crop(y: Tensor, lead_shape, m_real: int, n: int) -> Tensor:
+    y = y[:m_real].reshape(*lead_shape, n)
+    return y if y.is_contiguous() else y.contiguous()
+
+
+@torch.library.custom_op("quartet_b200::rmsnorm_linear_fwd", mutates_args=())
+def rmsnorm_linear_fwd(x: Tensor, gamma: Tensor, eps: float, w: Tensor, handle: int,
+                       out_dtype: torch.dtype) -> Tuple[Tensor, Tensor, Tensor, Tensor, Tensor, Tensor, Tensor, Tensor]:
+    """QuantizedLinear(RMSNorm(x)) with the norm of src/models/llama.py:64-75, `(x * rstd).type_as(x) * gamma`,
+    computed inside the forward quantizer: the normalised activation (fp32, whatever the dtype of x) is never
+    written.  Returns y, the packed operands the backward needs and rstd = rsqrt(mean(x^2) + eps) per row."""
+    layer = _layer(handle)
+    aq, wq = layer.activation_quantizer, layer.weight_quantizer
+    aq._see(gamma)  # the quantizer's input is the fp32 product
+    wq._see(w)
+    K = w.shape[1]
+    x2 = _pad_rows(x.reshape(-1, K).contiguous())
+    xc, xs, xm, rstd = ops.quant_fwd_rmsnorm(x2, gamma.contiguous(), eps, aq.had_scale, ops.QUEST_GAUSSIAN_SCALE, return_mask=True)
+    y, wc, ws, wm = _weight_and_gemm(xc, xs, w, wq, out_dtype)
+    m_real = x.numel() // K
+    return _crop(y, x.shape[:-1], m_real, w.shape[0]), xc, xs, xm, wc, ws, wm, rstd[:m_real].reshape(*x.shape[:-1], 1).contiguous()
+
+
+@rmsnorm_linear_fwd.register_fake
+def _(x, gamma, eps, w, handle, out_dtype):
+    N, K = w.shape
+    mp = _pad128(x.numel() // K)
+    return (x.new_empty((*x.shape[:-1], N), dtype=out_dtype), _u8(x, mp, K // 2), _u8(x, _sf_bytes(mp, K)), _u8(x, mp, K // 8),
+            _u8(x, N, K // 2), _u8(x, _sf_bytes(N, K)), _u8(x, N, K // 8), x.new_empty((*x.shape[:-1], 1), dtype=torch.float32))
+
+
+def _rmsnorm_linear_setup(ctx, inputs, output):
+    x, gamma, _, w, handle, _ = inputs
+    _, xc, xs, xm, wc, ws, wm, rstd = output
+    ctx.save_for_backward(xc, xs, xm, wc, ws, wm, rstd, x, gamma)
+    ctx.handle, ctx.w_dtype = handle, w.dtype
+    ctx.set_materialize_grads(False)
+
+
+def _rmsnorm_linear_backward(ctx, e, *unused):
+    if e is None:
+        return None, None, None, None, None, None
+    xc, xs, xm, wc, ws, wm, rstd, x, gamma = ctx.saved_tensors
+    need_x, need_g, need_w = ctx.needs_input_grad[0], ctx.needs_input_grad[1], ctx.needs_input_grad[3]
+    # gradient of the normalised activation (fp32), then the norm's own backward, step by step in the order autograd
+    # differentiates `(xf * rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps)).type_as(x) * gamma`: the round-to-nearest
+    # quantizers further up the backward pass turn a last-place difference in dx into different codes, so the
+    # same operations in the same order are what keeps this path equal to the unfused model
+    g, dw = torch.ops.quartet_b200.linear_bwd(e.contiguous(), xc, xs, xm, wc, ws, wm, ctx.handle, torch.float32, ctx.w_dtype,
+                                              need_x or need_g, need_w)
+    dx = dgamma = None
+    if need_x or need_g:
+        g = g.reshape(x.shape)
+        xf = x.float()
+        n_hat = (xf * rstd).type_as(x)
+        if need_g:
+            dgamma = (g * n_hat).sum(dim=tuple(range(g.dim() - 1))).to(gamma.dtype)
+        if need_x:
+            d_n = (g * gamma).to(x.dtype).float()                      # through `* gamma` and `.type_as(x)`
+            d_r = (d_n * xf).sum(-1, keepdim=True)                      # n = xf * r
+            d_m = (-0.5 * d_r) * rstd.pow(3)                            # r = rsqrt(m + eps)
+            d_p = d_m.expand_as(xf) / xf.shape[-1]                      # m = mean(p)
+            dx = (d_n * rstd + d_p * (2.0 * xf)).to(x.dtype)            # p = xf ** 2, both uses of xf
+    return dx, dgamma, None, (dw if need_w else None), None, None
+
+
+torch.library.register_autograd("quartet_b200::rmsnorm_linear_fwd", _rmsnorm_linear_backward, setup_context=_rmsnorm_linear_setup)
+
+
+@torch.library.custom_op("quartet_b200::swiglu_linear_fwd", mutates_args=())
+def swiglu_linear_fwd(h: Tensor, w: Tensor, handle: int, out_dtype: torch.dtype) -> Tuple[Tensor, Tensor, Tensor, Tensor, Tensor, Tensor, Tensor]:
+    """QuantizedLinear(silu(up) * gate) with up, gate the two halves of h's last axis (src/models/llama.py:112-114),
+    computed inside the forward quantizer: the product is never written."""
+    layer = _layer(handle)
+    aq, wq = layer.activation_quantizer, layer.weight_quantizer
+    aq._see(h)
+    wq._see(w)
+    K = w.shape[1]
+    h2 = _pad_rows(h.reshape(-1, 2 * K).contiguous())
+    xc, xs, xm = ops.quant_fwd_swiglu(h2, aq.had_scale, ops.QUEST_GAUSSIAN_SCALE, return_mask=True)
+    y, wc, ws, wm = _weight_and_gemm(xc, xs, w, wq, out_dtype)
+    return _crop(y, h.shape[:-1], h.numel() // (2 * K), w.shape[0]), xc, xs, xm, wc, ws, wm
+
+
+@swiglu_linear_fwd.register_fake
+def _(h, w, handle, out_dtype):
+    N, K = w.shape
+    mp = _pad128(h.numel() // (2 * K))
+    return (h.new_empty((*h.shape[:-1], N), dtype=out_dtype), _u8(h, mp, K // 2), _u8(h, _sf_bytes(mp, K)), _u8(h, mp, K // 8),
+            _u8(h, N, K // 2), _u8(h, _sf_bytes(N, K)), _u8(h, N, K // 8))
+
+
+def _swiglu_linear_setup(ctx, inputs, output):
+    h, w, handle, _ = inputs
+    _, xc, xs, xm, wc, ws, wm = output
+    ctx.save_for_backward(xc, xs, xm, wc, ws, wm, h)
+    ctx.handle, ctx.w_dtype = handle, w.dtype
+    ctx.set_materialize_grads(False)
+
+
+def _swiglu_linear_backward(ctx, e, *unused):
+    if e is None:
+        return None, None, None, None
+    xc, xs, xm, wc, ws, wm, h = ctx.saved_tensors
+    need_h, need_w = ctx.needs_input_grad[0], ctx.needs_input_grad[1]
+    g, dw = torch.ops.quartet_b200.linear_bwd(e.contiguous(), xc, xs, xm, wc, ws, wm, ctx.handle, h.dtype, ctx.w_dtype, need_h, need_w)
+    dh = None
+    if need_h:
+        # the operations autograd runs for `silu(up) * gate`, in h's dtype (see the note in the norm's backward)
+        K = h.shape[-1] // 2
+        g = g.reshape(*h.shape[:-1], K)
+        up, gate = h[..., :K], h[..., K:]
+        dh = torch.cat([torch.ops.aten.silu_backward(g * gate, up), g * torch.nn.functional.silu(up)], dim=-1)
+    return dh, (dw if need_w else None), None, None
+
+
+torch.library.register_autograd("quartet_b200::swiglu_linear_fwd", _swiglu_linear_backward, setup_context=_swiglu_linear_setup)

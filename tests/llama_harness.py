@@ -34,8 +34,12 @@ def rotary(q, k):
 
 
 class Block(nn.Module):
-    def __init__(self, Q, d, n_head, hidden, gkw, n_kv_head=None, eps=1e-6):
+    def __init__(self, Q, d, n_head, hidden, gkw, n_kv_head=None, eps=1e-6, fuse_producers=False):
         super().__init__()
+        # fuse_producers: the two norms and the SwiGLU product are computed inside the forward quantizer of the layer
+        # they feed (Q.rmsnorm_linear / Q.swiglu_linear) instead of as torch operations in front of it
+        self.fuse = fuse_producers
+        self.rmsnorm_linear, self.swiglu_linear = getattr(Q, "rmsnorm_linear", None), getattr(Q, "swiglu_linear", None)
 
         def lin(i, o):
             return Q.QuantizedLinear(
@@ -57,24 +61,30 @@ class Block(nn.Module):
     def forward(self, x):
         b, t, d = x.shape
         hd = d // self.n_head
-        q, k, v = self.c_attn(self.ln1(x)).split([d, self.kv_dim, self.kv_dim], dim=2)
+        if self.fuse:
+            qkv = self.rmsnorm_linear(x, self.ln1.weight, self.ln1.eps, self.c_attn)
+        else:
+            qkv = self.c_attn(self.ln1(x))
+        q, k, v = qkv.split([d, self.kv_dim, self.kv_dim], dim=2)
         q = q.view(b, t, self.n_head, hd).transpose(1, 2)
         k, v = (z.view(b, t, self.n_kv_head, hd).transpose(1, 2) for z in (k, v))
         q, k = rotary(q, k)
         y = F.scaled_dot_product_attention(q, k, v, is_causal=True, enable_gqa=self.n_kv_head != self.n_head)
         y = y.transpose(1, 2).reshape(b, t, d)
         x = x + self.attn_proj(y)
+        if self.fuse:
+            return x + self.swiglu_linear(self.rmsnorm_linear(x, self.ln2.weight, self.ln2.eps, self.w12), self.c_proj)
         up, gate = self.w12(self.ln2(x)).split(self.hidden, dim=-1)
         return x + self.c_proj(F.silu(up) * gate)
 
 
 class TinyLlama(nn.Module):
-    def __init__(self, Q, vocab=512, d=256, n_layer=2, n_head=2, multiple_of=128, gkw=None, n_kv_head=None, eps=1e-6):
+    def __init__(self, Q, vocab=512, d=256, n_layer=2, n_head=2, multiple_of=128, gkw=None, n_kv_head=None, eps=1e-6, fuse_producers=False):
         super().__init__()
         hidden = int(2 * 4 * d / 3)
         hidden = multiple_of * ((hidden + multiple_of - 1) // multiple_of)
         self.wte = nn.Embedding(vocab, d)
-        self.blocks = nn.ModuleList(Block(Q, d, n_head, hidden, gkw or {"stochastic": True, "rerotate": "signs"}, n_kv_head, eps)
+        self.blocks = nn.ModuleList(Block(Q, d, n_head, hidden, gkw or {"stochastic": True, "rerotate": "signs"}, n_kv_head, eps, fuse_producers)
                                     for _ in range(n_layer))
         self.ln_f, self.lm_head = RMSNorm(d, eps), nn.Linear(d, vocab, bias=False)
         for n_, p in self.named_parameters():

@@ -80,6 +80,27 @@ def test_layer_traces_to_one_operator_per_direction():
     assert dx.shape == (150, 256) and dx.dtype == torch.bfloat16 and dw.shape == (384, 256) and dw.dtype == torch.float32
 
 
+def test_producer_fused_layer_operators_trace():
+    """rmsnorm_linear_fwd / swiglu_linear_fwd (the layer with the step that produces its input inside the forward
+    quantizer): shape contracts of their fake kernels, on fake CUDA tensors (their backward needs a device's
+    autograd engine and is covered by the GPU tests)."""
+    from torch._subclasses.fake_tensor import FakeTensorMode
+
+    ln = _production_linear(256, 384)
+    proj = _production_linear(512, 256)
+    with FakeTensorMode():
+        x = torch.empty(3, 50, 256, dtype=torch.float32, device="cuda")
+        gamma = torch.empty(256, dtype=torch.float32, device="cuda")
+        w = torch.empty(384, 256, dtype=torch.float32, device="cuda")
+        out = T.rmsnorm_linear_fwd(x, gamma, 1e-5, w, ln._handle, torch.bfloat16)
+        assert out[0].shape == (3, 50, 384) and out[0].dtype == torch.bfloat16 and out[1].shape == (256, 128)
+        assert out[7].shape == (3, 50, 1) and out[7].dtype == torch.float32
+        h = torch.empty(3, 50, 1024, dtype=torch.bfloat16, device="cuda")
+        w2 = torch.empty(256, 512, dtype=torch.float32, device="cuda")
+        out = T.swiglu_linear_fwd(h, w2, proj._handle, torch.bfloat16)
+        assert out[0].shape == (3, 50, 256) and out[1].shape == (256, 256) and out[3].shape == (256, 64)
+
+
 def test_registry_names_and_module_attributes():
     assert len(Q.QUANTIZER_CLASSES) == 40
     assert set(Q.BACKWARD_SCHEMES) == {"EW_EtX", "Q(E)W_Q(Et)X", "Q(E)Q(Wt)t_Q(Et)Q(Xt)t"}

@@ -124,8 +124,12 @@ def test_reference_llama_trains_on_this_package(Q, compiled):
         assert ops.device_status() == 0
 
 
-def test_training_step_matches_the_reference_models_own_step(Q, golden_dir):
-    """tests/golden/llama_tiny_step.npz holds one fp32 training step of the REFERENCE'S OWN Llama (its model code,
+@pytest.mark.parametrize("fuse_producers", [False, True])
+def test_training_step_matches_the_reference_models_own_step(Q, golden_dir, fuse_producers):
+    """(fuse_producers: the norms and the SwiGLU product computed inside the forward quantizers,
+    Q.rmsnorm_linear / Q.swiglu_linear, held to the same comparison: their backward runs the operations autograd
+    runs for the unfused steps, in the same order, and on this input reproduces the unfused gradients bit for bit.)
+    tests/golden/llama_tiny_step.npz holds one fp32 training step of the REFERENCE'S OWN Llama (its model code,
     its quantization package, its kernel under the Triton interpreter; generator: tests/golden/make_model_golden.py).
     The harness model with the same parameters, its block linears served by this library, must reproduce the loss,
     the logits and every parameter's gradient.  Rounding is to nearest in the gradient quantizer, so nothing is
@@ -138,7 +142,7 @@ def test_training_step_matches_the_reference_models_own_step(Q, golden_dir):
 
     g = np.load(os.path.join(golden_dir, "llama_tiny_step.npz"))
     model = TinyLlama(Q, vocab=256, d=128, n_layer=2, n_head=1, multiple_of=256, gkw={"stochastic": False},
-                      eps=float(g["rmsnorm_eps"])).cuda()
+                      eps=float(g["rmsnorm_eps"]), fuse_producers=fuse_producers).cuda()
     assert model.blocks[0].hidden == 512
 
     def ref_name(n):  # harness parameter name -> the reference model's
@@ -176,4 +180,56 @@ def test_training_step_matches_the_reference_models_own_step(Q, golden_dir):
         worst = min(worst, (cos, n))
         assert cos > 0.9999, (n, cos)
     print("lowest first-row cosine", worst)
+    assert ops.device_status() == 0
+
+
+@pytest.mark.parametrize("compiled", [False, True])
+def test_producer_fused_blocks_match_the_plain_blocks(Q, compiled):
+    """The harness model with RMSNorm and SwiGLU computed inside the forward quantizers of the layers they feed
+    against the same model with the steps as torch operations, bf16 autocast, round-to-nearest gradients: the same
+    loss and gradients up to the quantization decisions that the last place of the norm's row statistic flips;
+    and the fused form traces under torch.compile and trains."""
+    from quartet_b200 import ops
+
+    torch.manual_seed(7)
+    gkw = {"stochastic": False, "rerotate": None}
+    plain = TinyLlama(Q, gkw=gkw).cuda()
+    fused = TinyLlama(Q, gkw=gkw, fuse_producers=True).cuda()
+    fused.load_state_dict(plain.state_dict())
+    with torch.no_grad():  # norm weights away from 1 so that their gradients and their use are both exercised
+        for m in (plain, fused):
+            torch.manual_seed(8)
+            for blk in m.blocks:
+                blk.ln1.weight.add_(0.1 * torch.randn_like(blk.ln1.weight))
+                blk.ln2.weight.add_(0.1 * torch.randn_like(blk.ln2.weight))
+    idx = torch.randint(0, 512, (4, 128), device="cuda")
+    tgt = torch.roll(idx, -1, 1)
+    runner = fused
+    if compiled:
+        torch._dynamo.reset()
+        runner = torch.compile(fused)
+    l_p = _step(plain, idx, tgt)
+    for p in fused.parameters():
+        p.grad = None
+    with torch.autocast("cuda", dtype=torch.bfloat16):
+        l_f = runner(idx, tgt)
+        l_f.backward()
+    print("loss plain", l_p.item(), "fused", l_f.item())
+    assert abs(l_p.item() - l_f.item()) < 2e-3 * abs(l_p.item())
+    for (n, a), (_, b) in zip(plain.named_parameters(), fused.named_parameters()):
+        assert b.grad is not None and torch.isfinite(b.grad).all(), n
+        cos = torch.nn.functional.cosine_similarity(a.grad.flatten().float(), b.grad.flatten().float(), dim=0).item()
+        # compiled: inductor evaluates the surrounding bf16 operations in another order, and some 4-bit decisions flip
+        assert cos > (0.85 if compiled else 0.99), (n, cos)
+    opt = torch.optim.AdamW(fused.parameters(), lr=3e-3)
+    losses = []
+    for _ in range(12):
+        for p in fused.parameters():
+            p.grad = None
+        with torch.autocast("cuda", dtype=torch.bfloat16):
+            loss = runner(idx, tgt)
+            loss.backward()
+        losses.append(loss.item())
+        opt.step()
+    assert losses[-1] < 0.85 * losses[0]
     assert ops.device_status() == 0
