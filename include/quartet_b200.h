@@ -46,7 +46,7 @@ enum { QUARTET_BF16 = 0, QUARTET_F32 = 1 };
 /* rounding modes of the backward (absmax-scaled) quantizers */
 enum {
     QUARTET_ROUND_NEAREST = 0,    /* AlbertTsengQuantizer(stochastic=False) */
-    QUARTET_ROUND_SR_PHILOX = 1,  /* stochastic, library's own Philox4x32-10 dither stream (seed, offset) */
+    QUARTET_ROUND_SR_PHILOX = 1,  /* stochastic, library's own Philox4x32-7 dither stream (seed, offset) */
     QUARTET_ROUND_SR_NOISE = 2,   /* stochastic, caller-supplied fp32 uniform noise tensor, reference `u < p` rule */
     QUARTET_ROUND_SR_TLRAND = 3   /* stochastic, reference-compatible stream: tl.rand(seed, flat_offset) */
 };

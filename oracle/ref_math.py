@@ -111,11 +111,14 @@ def triton_rand(seed: int, offsets: np.ndarray) -> torch.Tensor:
 _BITREV8 = np.array([int(f"{i:08b}"[::-1], 2) for i in range(256)], dtype=np.uint8)
 
 
+OWN_PHILOX_ROUNDS = 7  # the library's own dither stream (the reference-compatible tl.rand stream keeps Triton's ten)
+
+
 def own_dither16(seed: int, offset: int, n_groups: int) -> np.ndarray:
     """The library's own stochastic-rounding stream: a 16-bit dither per element.
 
     Group g (32 elements, numbered in the OUTPUT tensor's row-major order) uses
-    two Philox4x32-10 calls with key = seed, counter = (2g + j, g_hi, offset_lo,
+    two Philox4x32-7 calls (seven rounds) with key = seed, counter = (2g + j, g_hi, offset_lo,
     offset_hi), j = 0, 1.  Output word w of call j (bytes b0..b3, little end
     first) serves elements 16j + 4w .. 16j + 4w + 3 the way the hardware
     conversion consumes it (rev = byte bit-reversed):
@@ -134,6 +137,7 @@ def own_dither16(seed: int, offset: int, n_groups: int) -> np.ndarray:
             np.uint32((offset >> 32) & 0xFFFFFFFF),
             seed & 0xFFFFFFFF,
             (seed >> 32) & 0xFFFFFFFF,
+            rounds=OWN_PHILOX_ROUNDS,
         )
         for w in range(4):
             b = [((words[w] >> np.uint32(8 * k)) & np.uint32(0xFF)).astype(np.uint8) for k in range(4)]
