@@ -53,8 +53,8 @@ struct GemmCfg {
     static constexpr int TMEM_COLS = 512;
     static constexpr int STG_BYTES = 4 * 4096;              // epilogue staging, 4 KB per epilogue warp
     static constexpr int SMEM = STAGES * STAGE_BYTES + STG_BYTES + 512 + 1024;
-    static_assert(SF_COL0 + STAGES * SF_COLS <= TMEM_COLS, "tensor memory budget");
-    static_assert(SMEM <= 232448, "shared memory budget");
+    static_assert(SF_COL0 + STAGES * SF_COLS <= TMEM_COLS, "tensor memory capacity");
+    static_assert(SMEM <= 232448, "shared memory capacity");
 };
 
 struct GemmParams {
@@ -467,7 +467,7 @@ struct Gemm2Cfg {
     static constexpr int STG_BYTES = 8 * NSTG * 2048;        // epilogue staging: NSTG buffers of 2 KB per epilogue warp (8 warps)
     static constexpr int STAGES = (232448 - STG_BYTES - 512) / STAGE_BYTES;
     static constexpr int SMEM = STAGES * STAGE_BYTES + STG_BYTES + 512;
-    static_assert(SF_COL0 + SF_SLOTS * SF_COLS <= TMEM_COLS, "tensor memory budget");
+    static_assert(SF_COL0 + SF_SLOTS * SF_COLS <= TMEM_COLS, "tensor memory capacity");
     static_assert(SF_SLOTS < STAGES, "scale slots are recycled through the stage barriers");
     static_assert(B_BYTES % 1024 == 0, "operand stages stay 1024-byte aligned");
 };
