@@ -74,8 +74,7 @@ int quartet_quant_fwd(const void* x, int x_dtype, int64_t rows, int64_t cols, fl
  *   (x * rsqrt(mean(x^2) + eps)).type_as(x) * weight      (weight: fp32 [cols]; result fp32),
  * feeding c_attn (llama.py:124) and mlp.w12 (llama.py:113).  x: [rows, cols] bf16 / fp32,
  * cols % 128 == 0.  rstd ([rows] fp32, required) receives rsqrt(mean(x^2) + eps) per row: the
- * norm's backward needs it.  Two launches per chunk of rows (statistics, then quantization; the
- * chunk is sized for the second read to come from L2).
+ * norm's backward needs it.  Two launches: the statistics, then the quantization (each reads the rows).
  * quartet_rms_stats: the statistics alone (cols % 8 == 0).
  *
  * quartet_quant_fwd_swiglu: the input is silu(h[:, :hidden]) * h[:, hidden:] (llama.py:112-114,

@@ -85,9 +85,9 @@ __device__ __forceinline__ void unpack_bf16x8(const uint4& q, float* out) {
 // One group of 32 consecutive row elements out of a 128-row tile that TMA laid down as 128-byte-wide
 // boxes (128 rows x 128 B each, 128B swizzle: 16-byte chunk c of row r sits at chunk c ^ (r & 7)).
 // `gk` = group index within the tile row (0..3).
-template <bool F32>
-__device__ __forceinline__ void load_row_group(const uint8_t* s_in, int row, int gk, float (&w)[32]) {
-    constexpr int BOX = 128 * 128;
+// BOX = bytes of one box (its rows x 128): 128-row boxes for the 128 x 128 tiles, fewer rows for wider tiles.
+template <bool F32, int BOX>
+__device__ __forceinline__ void load_row_group_box(const uint8_t* s_in, int row, int gk, float (&w)[32]) {
     if (F32) {
         const uint8_t* base = s_in + gk * BOX + row * 128;
 #pragma unroll
@@ -104,6 +104,10 @@ __device__ __forceinline__ void load_row_group(const uint8_t* s_in, int row, int
             unpack_bf16x8(q, &w[8 * j]);
         }
     }
+}
+template <bool F32>
+__device__ __forceinline__ void load_row_group(const uint8_t* s_in, int row, int gk, float (&w)[32]) {
+    load_row_group_box<F32, 128 * 128>(s_in, row, gk, w);
 }
 
 // ---------------------------------------------------------------------------

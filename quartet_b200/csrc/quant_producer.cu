@@ -11,8 +11,13 @@
 // rms_stats_kernel reads the rows once and writes rstd (which the backward pass of the norm needs anyway), the
 // quantizer reads them again, last rows first, so that what the first pass left in L2 is found there.  Bytes
 // per element with fp32 rows: 4 + 4 read, 0.66 written, against 4 + 4 (the norm's own read and write) + 4 + 0.66
-// for the norm followed by the plain quantizer.  (Walking the tensor in chunks of 20-80 MB, statistics then
-// quantization per chunk, was measured slower: the second read of a chunk still came from DRAM.)
+// for the norm followed by the plain quantizer.
+// Measured and dropped: (1) walking the tensor in chunks of 20-80 MB, statistics then quantization per chunk
+// (slower: the second read of a chunk still came from DRAM); (2) two single-read forms, in which the CTAs that
+// share a band of rows exchange their tiles' sums of squares while the tiles wait in shared memory -- through
+// global memory in a cooperative launch, and through distributed shared memory in a cluster of up to 8.  Neither
+// was faster than the two launches: the exchange sits between a tile's load and its arithmetic, and with three
+// or four CTAs per SM too few loads stay in flight.
 #include "common.cuh"
 #include "quant_math.cuh"
 
@@ -328,7 +333,6 @@ extern "C" __attribute__((visibility("default"))) int quartet_quant_fwd_rmsnorm(
     if (rc) return rc;
     const bool f32 = x_dtype == QUARTET_F32;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    if ((rc = launch_stats(x, x_dtype, rows, cols, eps, rstd, s))) return rc;
     ProducerParams p{};
     p.rows = rows, p.cols = cols, p.sf = sf;
     p.sf_blocks_per_rowblock = (cols / 32 + 3) / 4;
@@ -336,6 +340,8 @@ extern "C" __attribute__((visibility("default"))) int quartet_quant_fwd_rmsnorm(
     p.has_mask = mask != nullptr;
     p.box_rows = (uint32_t)(rows < P_TILE_R ? rows : P_TILE_R);
     p.rstd = rstd, p.gamma = weight;
+    // two passes: the row statistics, then the quantizer
+    if ((rc = launch_stats(x, x_dtype, rows, cols, eps, rstd, s))) return rc;
     p.reverse_rows = 1;  // the rows the statistics pass read last are the likeliest to be in L2 still
     return f32 ? launch_producer<PRO_RMSNORM, true>(x, nullptr, cols, p, codes, mask, s)
                : launch_producer<PRO_RMSNORM, false>(x, nullptr, cols, p, codes, mask, s);
