@@ -115,3 +115,25 @@ def test_own_stream_is_unbiased():
     q2 = rm.quant_bwd_own(x, h, 0, seed=123, offset=0)
     assert bool((q.codes == q2.codes).all())
     assert int(q.idx.max()) <= 7 and int(q.idx.min()) >= 0
+
+
+@pytest.mark.parametrize("name", ["f32", "bf16"])
+def test_producer_steps_equal_the_reference_models_own(golden_dir, name):
+    """oracle.ref_math.rmsnorm / swiglu against the reference's `RMSNorm` module and `LlamaMLP.forward`
+    (src/models/llama.py:64-75, 112-114; fixture tests/golden/producer_steps.npz, generator
+    tests/golden/make_producer_golden.py): bit for bit, fp32 and bf16 inputs."""
+    g = np.load(os.path.join(golden_dir, "producer_steps.npz"))
+
+    def tensor(key):
+        a = torch.from_numpy(g[key])
+        return a.view(torch.bfloat16) if a.dtype == torch.int16 else a
+
+    x, want = tensor(f"rms_x_{name}"), tensor(f"rms_out_{name}")
+    got = rm.rmsnorm(x, torch.from_numpy(g["rms_weight"]), float(g["rms_eps"]))
+    assert got.dtype == torch.float32 and torch.equal(got, want)
+    # with the row statistic handed in (what the device tests do), the remaining steps give the same bits
+    rstd = torch.rsqrt(x.float().pow(2).mean(-1) + float(g["rms_eps"]))
+    assert torch.equal(rm.rmsnorm(x, torch.from_numpy(g["rms_weight"]), float(g["rms_eps"]), rstd=rstd), want)
+    h, want = tensor(f"swiglu_h_{name}"), tensor(f"swiglu_out_{name}")
+    got = rm.swiglu(h)
+    assert got.dtype == h.dtype and torch.equal(got.float(), want.float())
