@@ -173,3 +173,23 @@ def test_reference_model_code_resolves_to_this_package():
             assert type(m.backward_scheme).__name__ == "QEQWtt_QEtQXtt_Scheme" and m.bias is None
         assert not isinstance(model.lm_head, Q.QuantizedLinear)
         assert sum(p.numel() for p in model.parameters()) > 70_000_000  # 30.5 M in the blocks, untied 32000 x 640 embeddings twice
+
+
+def test_producer_calls_fall_back_to_the_separate_steps():
+    """Where the fused form does not apply (here: CPU tensors, un-quantized layers), rmsnorm_linear / swiglu_linear are
+    the norm / activation followed by the layer, gradients included."""
+    torch.manual_seed(0)
+    lin = Q.QuantizedLinear(64, 48, bias=False)
+    x = torch.randn(3, 7, 64, requires_grad=True)
+    gamma = (1.0 + 0.1 * torch.randn(64)).requires_grad_(True)
+    y = Q.rmsnorm_linear(x, gamma, 1e-5, lin)
+    want = lin((x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + 1e-5)) * gamma)
+    assert torch.allclose(y, want, atol=1e-6)
+    y.sum().backward()
+    assert x.grad is not None and gamma.grad is not None and lin.weight.grad is not None
+    proj = Q.QuantizedLinear(32, 16, bias=False)
+    h = torch.randn(5, 64, requires_grad=True)
+    z = Q.swiglu_linear(h, proj)
+    assert torch.allclose(z, proj(torch.nn.functional.silu(h[:, :32]) * h[:, 32:]), atol=1e-6)
+    z.sum().backward()
+    assert h.grad is not None and h.grad.shape == h.shape
