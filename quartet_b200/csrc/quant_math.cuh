@@ -243,6 +243,33 @@ __device__ __forceinline__ uint32_t spread_sign_bits(uint32_t s8) {
 // report which values lie strictly inside the grid (|v| < 6) as 32 mask bits.  w holds the group on entry and
 // the rotated values on return.  ROT = false skips the rotation (h must then be 1).
 // ---------------------------------------------------------------------------
+// The part after the moments: w holds the rotated values WITHOUT the factor h; mean and mean_sq are the moments of
+// the rotated group with it.
+__device__ __forceinline__ void quest_finish_group(const float (&w)[32], float h, float mean, float mean_sq, float gaussian_scale,
+                                                   uint32_t (&words)[4], uint32_t& mbits, int& e8m0) {
+    const float var = fmaxf(mean_sq - mean * mean, 0.f);
+    const float scales = gaussian_scale * sqrtf(var) + 1e-8f;
+    e8m0 = exp_field(scales);
+    const float c = h * pow2_biased(254 - e8m0);  // h * 2^-e
+    float v[32];
+    const f32x2_t c2 = pack2(c, c), m36 = pack2(-36.f, -36.f);
+    // mask bit = |v| < 6  <=>  v * v - 36 < 0; the fused multiply-add rounds the exact difference, so its
+    // sign is exact (and |v| == 6 gives +0: clipped, as in the reference's strict `<`)
+    mbits = 0;
+#pragma unroll
+    for (int i = 15; i >= 0; --i) {
+        const f32x2_t vp = mul2(pack2(w[2 * i], w[2 * i + 1]), c2);
+        unpack2(vp, v[2 * i], v[2 * i + 1]);
+        float t0, t1;
+        unpack2(fma2(vp, vp, m36), t0, t1);
+        mbits = __funnelshift_l(__float_as_uint(t1), mbits, 1);
+        mbits = __funnelshift_l(__float_as_uint(t0), mbits, 1);
+    }
+#pragma unroll
+    for (int q = 0; q < 4; ++q) words[q] = cvt_e2m1x8_ties_down(&v[8 * q]);
+    // (the reference gives exact zeros a minus sign, `v > 0 ? + : -`; here +0 stays +0)
+}
+
 template <bool ROT>
 __device__ __forceinline__ void quest_quantize_group(float (&w)[32], float h, float gaussian_scale, uint32_t (&words)[4],
                                                      uint32_t& mbits, int& e8m0) {
@@ -267,32 +294,12 @@ __device__ __forceinline__ void quest_quantize_group(float (&w)[32], float h, fl
     unpack2(acc, s_even, s_odd);
     const float sumsq = s_even + s_odd;
     if (ROT) wht32(w);
-
     // rotated: sum_j xh_j = 32 h x_0 and sum_j xh_j^2 = 32 h^2 sum_i x_i^2; un-rotated (h = 1): the plain moments
     const float mean = ROT ? h * x0 : x0;
     const float mean_sq = ROT ? (h * h) * sumsq : sumsq * (1.0f / 32.0f);
-    const float var = fmaxf(mean_sq - mean * mean, 0.f);
-    const float scales = gaussian_scale * sqrtf(var) + 1e-8f;
-    e8m0 = exp_field(scales);
-    const float c = h * pow2_biased(254 - e8m0);  // h * 2^-e
-    float v[32];
-    const f32x2_t c2 = pack2(c, c), m36 = pack2(-36.f, -36.f);
-    // mask bit = |v| < 6  <=>  v * v - 36 < 0; the fused multiply-add rounds the exact difference, so its
-    // sign is exact (and |v| == 6 gives +0: clipped, as in the reference's strict `<`)
-    mbits = 0;
-#pragma unroll
-    for (int i = 15; i >= 0; --i) {
-        const f32x2_t vp = mul2(pack2(w[2 * i], w[2 * i + 1]), c2);
-        unpack2(vp, v[2 * i], v[2 * i + 1]);
-        float t0, t1;
-        unpack2(fma2(vp, vp, m36), t0, t1);
-        mbits = __funnelshift_l(__float_as_uint(t1), mbits, 1);
-        mbits = __funnelshift_l(__float_as_uint(t0), mbits, 1);
-    }
-#pragma unroll
-    for (int q = 0; q < 4; ++q) words[q] = cvt_e2m1x8_ties_down(&v[8 * q]);
-    // (the reference gives exact zeros a minus sign, `v > 0 ? + : -`; here +0 stays +0)
+    quest_finish_group(w, h, mean, mean_sq, gaussian_scale, words, mbits, e8m0);
 }
+
 
 // ---------------------------------------------------------------------------
 // Backward (absmax-scaled) quantization of one rotated group.
