@@ -15,7 +15,9 @@
  *                                 {0, .5, 1, 1.5, 2, 3, 4, 6}
  *   sf     uint8, E8M0 (value 2^(b-127)), one per 32 elements of a row, stored
  *          in 512-byte blocks of 128 rows x 4 scales; logical shape
- *          [pad128(rows), pad4(cols/32)]; byte offset = quartet_sf_offset()
+ *          [pad128(rows), pad4(cols/32)]; byte offset = quartet_sf_offset().
+ *          The row-wise quantizers write 0 for the padding rows of the last
+ *          128-row block.
  *   mask   uint8 [rows, cols/8]   1 bit per element, LSB first; 1 = |v| < 6
  *
  * Reference paths are given relative to the reference project root.

@@ -163,7 +163,8 @@ __global__ void __launch_bounds__(P_THREADS, producer_min_ctas<PRO, F32>())
         quest_quantize_group<true>(w, h, p.gaussian_scale, words, mbits, e8m0);
         *reinterpret_cast<uint4*>(s_codes + row * 64 + ((gk ^ ((row >> 1) & 3)) << 4)) = make_uint4(words[0], words[1], words[2], words[3]);
         *reinterpret_cast<uint32_t*>(s_mask + row * 16 + gk * 4) = mbits;
-        s_sf[(row & 31) * 16 + (row >> 5) * 4 + gk] = (uint8_t)e8m0;
+        // rows past the tensor's last one (padding of the 128-row scale block) get scale byte 0, whatever the tile held there
+        s_sf[(row & 31) * 16 + (row >> 5) * 4 + gk] = grow < p.rows ? (uint8_t)e8m0 : (uint8_t)0;
     }
 
     fence_proxy_async_smem();

@@ -105,7 +105,8 @@ __global__ void __launch_bounds__(ROWS_THREADS, F32 ? 3 : 4) quant_rows_kernel(c
         // the store expects; a quarter-warp's eight 16-byte stores then fall into eight different bank groups
         *reinterpret_cast<uint4*>(s_codes + row * 64 + ((gk ^ ((row >> 1) & 3)) << 4)) = make_uint4(words[0], words[1], words[2], words[3]);
         if (KIND == KIND_QUEST) *reinterpret_cast<uint32_t*>(s_mask + row * 16 + gk * 4) = mbits;
-        s_sf[(row & 31) * 16 + (row >> 5) * 4 + gk] = (uint8_t)e8m0;
+        // rows past the tensor's last one (padding of the 128-row scale block) get scale byte 0, whatever the tile held there
+        s_sf[(row & 31) * 16 + (row >> 5) * 4 + gk] = grow < p.rows ? (uint8_t)e8m0 : (uint8_t)0;
     }
 
     fence_proxy_async_smem();
